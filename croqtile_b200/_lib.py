@@ -1,0 +1,96 @@
+"""ctypes binding of ``libcroq_b200.so`` (declared in ``include/croq_b200.h``).
+
+The library is the product: there is no Python or CPU fallback. Loading fails
+with an explicit error when the shared object has not been built, and every
+call that returns a non-zero status raises :class:`CroqError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_int, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcroq_b200.so"
+
+
+class View1(Structure):
+    """Layout of ``croq_view1`` / ``choreo::spanned_view<T,1>``."""
+    _fields_ = [("ptr", c_void_p), ("dims", c_size_t * 1)]
+
+
+class View2(Structure):
+    """Layout of ``croq_view2`` / ``choreo::spanned_view<T,2>``."""
+    _fields_ = [("ptr", c_void_p), ("dims", c_size_t * 2)]
+
+
+class View3(Structure):
+    """Layout of ``croq_view3`` / ``choreo::spanned_view<T,3>``."""
+    _fields_ = [("ptr", c_void_p), ("dims", c_size_t * 3)]
+
+
+STATUS = {
+    0: "CROQ_OK", 1: "CROQ_ERR_NULL", 2: "CROQ_ERR_SHAPE", 3: "CROQ_ERR_ALIGN",
+    4: "CROQ_ERR_CUDA", 5: "CROQ_ERR_TIMEOUT", 6: "CROQ_ERR_SCHEDULE",
+    7: "CROQ_ERR_INDEX", 8: "CROQ_ERR_UNSUPPORTED", 9: "CROQ_ERR_NO_DEVICE",
+}
+CROQ_DTYPE_F16 = 0
+CROQ_DTYPE_BF16 = 1
+
+P1, P2, P3 = POINTER(View1), POINTER(View2), POINTER(View3)
+
+# name -> (restype, argtypes); must list every symbol include/croq_b200.h declares.
+SIGNATURES = {
+    "croq_status_string": (c_char_p, [c_int]),
+    "croq_last_error_string": (c_char_p, []),
+    "croq_version": (c_char_p, []),
+    "croq_synchronize": (c_int, [c_void_p]),
+    "croq_matmul_f16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
+    "croq_matmul_bf16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
+    "croq_blockscale_gemm_e4m3": (c_int, [P2, P2, P2, P2, P2, c_int, c_void_p]),
+    "croq_gemm_sp_f16": (c_int, [P2, P2, P2, P2, c_int, c_void_p]),
+    "croq_moe_route_topk": (c_int, [P2, c_int, c_int, P2, P2, P1, P1, P1, P1, c_void_p]),
+    "croq_moe_permute": (c_int, [P2, P1, c_int, P2, c_void_p]),
+    "croq_moe_permute_quant_e4m3": (c_int, [P2, P1, c_int, P2, P2, c_void_p]),
+    "croq_moe_unpermute": (c_int, [P2, P1, P2, P2, c_void_p]),
+    "croq_moe_grouped_gemm_e4m3": (c_int, [P2, P2, P3, P3, P1, P2, c_int, c_void_p]),
+    "croq_quant_rows_e4m3": (c_int, [P2, P2, P2, c_void_p]),
+}
+
+
+class CroqError(RuntimeError):
+    """A libcroq_b200 entry point returned a non-zero status."""
+
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        self.name = STATUS.get(status, f"status {status}")
+        msg = f"{where}: {self.name}"
+        if detail:
+            msg += f" ({detail})"
+        super().__init__(msg)
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once and attaches the C signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m croqtile_b200.build` "
+            "(there is no fallback path)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        detail = load().croq_last_error_string().decode(errors="replace")
+        raise CroqError(status, where, detail)

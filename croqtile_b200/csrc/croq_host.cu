@@ -1,0 +1,198 @@
+// Per-device state, error text, status strings and tensor-map encoding.
+#include "croq_host.h"
+
+#include <mutex>
+#include <stdio.h>
+#include <string.h>
+
+#include "croq_device.cuh"
+
+namespace croq {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+DeviceState g_states[kMaxDevices];
+thread_local char g_error_text[512] = "";
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+// The driver entry point is fetched through the runtime so that the library
+// carries no link-time dependency on libcuda.
+int load_encode_fn() {
+  if (g_encode_tiled != nullptr) return CROQ_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult query;
+  cudaError_t err =
+      cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+  if (err != cudaSuccess) return record_cuda_error(err, "cudaGetDriverEntryPoint");
+  if (fn == nullptr || query != cudaDriverEntryPointSuccess)
+    return record_text_error(CROQ_ERR_CUDA, "cuTensorMapEncodeTiled not found in the driver");
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  return CROQ_OK;
+}
+
+}  // namespace
+
+int record_cuda_error(cudaError_t err, const char* what) {
+  snprintf(g_error_text, sizeof(g_error_text), "%s: %s (%s)", what, cudaGetErrorString(err),
+           cudaGetErrorName(err));
+  cudaGetLastError();  // clear the sticky-less error so later calls start clean
+  return CROQ_ERR_CUDA;
+}
+
+int record_text_error(int status, const char* what) {
+  snprintf(g_error_text, sizeof(g_error_text), "%s", what);
+  return status;
+}
+
+DeviceState* device_state(int* status_out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) {
+    *status_out = record_cuda_error(err, "cudaGetDevice");
+    return nullptr;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    *status_out = record_text_error(CROQ_ERR_NO_DEVICE, "device ordinal out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* st = &g_states[dev];
+  if (st->device == dev) {
+    *status_out = CROQ_OK;
+    return st;
+  }
+  cudaDeviceProp prop;
+  err = cudaGetDeviceProperties(&prop, dev);
+  if (err != cudaSuccess) {
+    *status_out = record_cuda_error(err, "cudaGetDeviceProperties");
+    return nullptr;
+  }
+  if (prop.major != 10) {
+    *status_out = record_text_error(
+        CROQ_ERR_NO_DEVICE, "libcroq_b200 needs an sm_100 device (tcgen05/TMEM); none is current");
+    return nullptr;
+  }
+  int* host = nullptr;
+  err = cudaHostAlloc(reinterpret_cast<void**>(&host), 64, cudaHostAllocMapped);
+  if (err != cudaSuccess) {
+    *status_out = record_cuda_error(err, "cudaHostAlloc(status word)");
+    return nullptr;
+  }
+  memset(host, 0, 64);
+  int* devp = nullptr;
+  err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&devp), host, 0);
+  if (err != cudaSuccess) {
+    cudaFreeHost(host);
+    *status_out = record_cuda_error(err, "cudaHostGetDevicePointer");
+    return nullptr;
+  }
+  int rc = load_encode_fn();
+  if (rc != CROQ_OK) {
+    cudaFreeHost(host);
+    *status_out = rc;
+    return nullptr;
+  }
+  st->sm_count = prop.multiProcessorCount;
+  st->cc_major = prop.major;
+  st->status_host = host;
+  st->status_dev = devp;
+  st->device = dev;
+  *status_out = CROQ_OK;
+  return st;
+}
+
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_bytes,
+                         const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         uint32_t box_cols) {
+  int rc = load_encode_fn();
+  if (rc != CROQ_OK) return rc;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult res = g_encode_tiled(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    char text[160];
+    snprintf(text, sizeof(text),
+             "cuTensorMapEncodeTiled(2d rows=%llu cols=%llu box=%ux%u) failed with CUresult %d",
+             (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols, (int)res);
+    return record_text_error(CROQ_ERR_CUDA, text);
+  }
+  return CROQ_OK;
+}
+
+int encode_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_bytes,
+                         const void* base, uint64_t batch, uint64_t rows, uint64_t cols,
+                         uint32_t box_rows, uint32_t box_cols) {
+  int rc = load_encode_fn();
+  if (rc != CROQ_OK) return rc;
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * elem_bytes, rows * cols * elem_bytes};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult res = g_encode_tiled(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    char text[160];
+    snprintf(text, sizeof(text),
+             "cuTensorMapEncodeTiled(3d batch=%llu rows=%llu cols=%llu) failed with CUresult %d",
+             (unsigned long long)batch, (unsigned long long)rows, (unsigned long long)cols,
+             (int)res);
+    return record_text_error(CROQ_ERR_CUDA, text);
+  }
+  return CROQ_OK;
+}
+
+}  // namespace croq
+
+extern "C" {
+
+const char* croq_status_string(int status) {
+  switch (status) {
+    case CROQ_OK: return "ok";
+    case CROQ_ERR_NULL: return "null view or data pointer";
+    case CROQ_ERR_SHAPE: return "tensor extents disagree";
+    case CROQ_ERR_ALIGN: return "pointer or row pitch not 16-byte aligned";
+    case CROQ_ERR_CUDA: return "CUDA call failed";
+    case CROQ_ERR_TIMEOUT: return "device-side wait ran out";
+    case CROQ_ERR_SCHEDULE: return "schedule entry outside the tile grid";
+    case CROQ_ERR_INDEX: return "routing or permutation index out of range";
+    case CROQ_ERR_UNSUPPORTED: return "unsupported argument combination";
+    case CROQ_ERR_NO_DEVICE: return "no sm_100 device is current";
+    default: return "unknown status";
+  }
+}
+
+const char* croq_last_error_string(void) { return croq::g_error_text; }
+
+const char* croq_version(void) { return "0.1.0"; }
+
+int croq_synchronize(croq_stream stream) {
+  int rc = CROQ_OK;
+  croq::DeviceState* st = croq::device_state(&rc);
+  if (st == nullptr) return rc;
+  cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return croq::record_cuda_error(err, "cudaStreamSynchronize");
+  int dev_status = *reinterpret_cast<volatile int*>(st->status_host);
+  if (dev_status == croq::kDevOk) return CROQ_OK;
+  *reinterpret_cast<volatile int*>(st->status_host) = 0;
+  switch (dev_status) {
+    case croq::kDevTimeout: return croq::record_text_error(CROQ_ERR_TIMEOUT, "a kernel wait ran out of its time budget");
+    case croq::kDevBadSchedule: return croq::record_text_error(CROQ_ERR_SCHEDULE, "a schedule entry lies outside the tile grid");
+    default: return croq::record_text_error(CROQ_ERR_INDEX, "a routing or permutation index is out of range");
+  }
+}
+
+}  // extern "C"

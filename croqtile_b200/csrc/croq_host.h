@@ -1,0 +1,55 @@
+// Host-side plumbing shared by the entry points: per-device state (SM count,
+// the status word kernels report into), CUDA error capture, view checks and
+// TMA tensor-map encoding. The checks restate what the reference's emitted
+// wrapper verifies before launch (lib/Target/GPU/cute_codegen.cpp:9896-9961).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/croq_b200.h"
+
+namespace croq {
+
+struct DeviceState {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status_host = nullptr;  // pinned, mapped: kernels write, host reads
+  int* status_dev = nullptr;   // device alias of status_host
+};
+
+// State of the current device; created on first use. Returns nullptr and
+// records the error when CUDA fails or the device is not sm_100.
+DeviceState* device_state(int* status_out);
+
+// Remembers a failed CUDA call for croq_last_error_string(); returns CROQ_ERR_CUDA.
+int record_cuda_error(cudaError_t err, const char* what);
+int record_text_error(int status, const char* what);
+
+#define CROQ_CUDA_TRY(expr)                                             \
+  do {                                                                  \
+    cudaError_t croq_err__ = (expr);                                    \
+    if (croq_err__ != cudaSuccess) return ::croq::record_cuda_error(croq_err__, #expr); \
+  } while (0)
+
+inline bool view_ok(const croq_view1* v) { return v != nullptr && v->ptr != nullptr; }
+inline bool view_ok(const croq_view2* v) { return v != nullptr && v->ptr != nullptr; }
+inline bool view_ok(const croq_view3* v) { return v != nullptr && v->ptr != nullptr; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Encodes a 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements
+// for tiled loads of box_rows x box_cols elements with the 128-byte swizzle.
+// box_cols * elem_bytes must be 128. Out-of-range parts of a box read zero.
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_bytes,
+                         const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         uint32_t box_cols);
+
+// Same for a 3-D tensor [batch, rows, cols]; a box covers one batch entry.
+int encode_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_bytes,
+                         const void* base, uint64_t batch, uint64_t rows, uint64_t cols,
+                         uint32_t box_rows, uint32_t box_cols);
+
+}  // namespace croq

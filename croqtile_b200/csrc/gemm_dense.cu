@@ -1,0 +1,354 @@
+// Persistent, warp-specialised f16 / bf16 GEMM for sm_100a.
+//
+//   output[m,n] = RN( sum_k lhs[m,k] * rhs[n,k] ),  fp32 accumulation in TMEM.
+//
+// Replaces the kernels the reference emits for `matmul_persis_hilbert_sm90`
+// and `matmul_f16_ws_1p3c_persis` (tests/gpu/end2end/wgmma_persis.co:5-92).
+// Same contract: tiles are visited in the order the caller's schedule_m /
+// schedule_n arrays give, work item = iteration * #CTAs + cta. The reference
+// keeps one warpgroup of WGMMA consumers per 64x128 tile; here one CTA owns a
+// 128x256 accumulator in tensor memory and three roles run concurrently:
+//   warp 0    TMA producer: global -> 128B-swizzled shared ring (kStages deep)
+//   warp 1    MMA issuer: tcgen05.mma 128x256x16, accumulators double-buffered
+//             in TMEM so the next tile's main loop overlaps this tile's epilogue
+//   warps 4-7 epilogue: tcgen05.ld -> cvt.rn -> 16-byte global stores
+// A schedule tile larger than 128x256 is walked as consecutive work items.
+#include "croq_device.cuh"
+#include "croq_host.h"
+
+namespace croq {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;   // 64 x 2 B = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 256;
+constexpr int kTmemCols = 512;  // two 256-column fp32 accumulators
+constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
+constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+
+struct DenseParams {
+  uint16_t* out;
+  int M, N, K;
+  const int* sched_m;
+  const int* sched_n;
+  int tile_m, tile_n;    // schedule tile extents
+  int tiles_m, tiles_n;  // schedule grid
+  int sub_m, sub_n;      // kernel tiles per schedule tile
+  int total_work;
+  int* status;
+};
+
+struct WorkTile {
+  int m0, n0, m_end, n_end;
+  bool valid;
+};
+
+__device__ __forceinline__ WorkTile decode_work(const DenseParams& p, int w) {
+  WorkTile t;
+  const int subs = p.sub_m * p.sub_n;
+  const int tile_id = w / subs;
+  const int s = w - tile_id * subs;
+  int bm, bn;
+  if (p.sched_m != nullptr) {
+    bm = __ldg(p.sched_m + tile_id);
+    bn = __ldg(p.sched_n + tile_id);
+  } else {
+    bm = tile_id / p.tiles_n;
+    bn = tile_id - bm * p.tiles_n;
+  }
+  if (bm < 0 || bm >= p.tiles_m || bn < 0 || bn >= p.tiles_n) {
+    *p.status = kDevBadSchedule;
+    t.valid = false;
+    t.m0 = t.n0 = t.m_end = t.n_end = 0;
+    return t;
+  }
+  const int si = s / p.sub_n;
+  const int sj = s - si * p.sub_n;
+  t.m0 = bm * p.tile_m + si * kBlockM;
+  t.n0 = bn * p.tile_n + sj * kBlockN;
+  t.m_end = min(p.M, (bm + 1) * p.tile_m);
+  t.n_end = min(p.N, (bn + 1) * p.tile_n);
+  t.valid = (t.m0 < t.m_end) && (t.n0 < t.n_end);
+  return t;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
+                  const __grid_constant__ CUtensorMap map_b, const DenseParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_drain;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      const WorkTile t = decode_work(p, w);
+      if (!t.valid) continue;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_2d(a_dst, &map_a, full, kb * kBlockK, t.m0);
+          tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, t.n0);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok) {
+      // Copies already issued still target this CTA's shared memory: give
+      // them a bounded moment to land before the CTA retires.
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 1000000ull) {
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    constexpr uint32_t idesc =
+        umma_idesc(kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16, kBlockM, kBlockN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      const WorkTile t = decode_work(p, w);
+      if (!t.valid) continue;
+      ok = mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_src = smem_base + stage * kStageBytes;
+          const uint64_t adesc = umma_desc_k_sw128(a_src);
+          const uint64_t bdesc = umma_desc_k_sw128(a_src + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // +32 bytes along K inside the swizzle row = +2 in 16-byte units
+            umma_f16(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bar_empty[stage]));
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(smem_u32(&bar_acc_full[acc]));
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    // Whatever was issued must retire before TMEM is released.
+    if (lane == 0) umma_commit(smem_u32(&bar_drain));
+    __syncwarp();
+    mbar_wait(smem_u32(&bar_drain), 0, abort_ptr);
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      const WorkTile t = decode_work(p, w);
+      if (!t.valid) continue;
+      ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = t.m0 + quarter * 32 + lane;
+      const uint32_t taddr =
+          tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = t.n0 + c * 32;
+        if (row < t.m_end && col0 < t.n_end) {
+          if (vec_ok && col0 + 32 <= t.n_end) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + i < t.n_end) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+}
+
+int check_dense_views(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                      const croq_view1* schedule_m, const croq_view1* schedule_n,
+                      int sched_tile_m, int sched_tile_n) {
+  if (!view_ok(lhs) || !view_ok(rhs) || !view_ok(output)) return CROQ_ERR_NULL;
+  const bool has_m = schedule_m != nullptr, has_n = schedule_n != nullptr;
+  if (has_m != has_n) return CROQ_ERR_NULL;
+  if (has_m && (!view_ok(schedule_m) || !view_ok(schedule_n))) return CROQ_ERR_NULL;
+  const size_t M = lhs->dims[0], K = lhs->dims[1], N = rhs->dims[0];
+  if (rhs->dims[1] != K || output->dims[0] != M || output->dims[1] != N) return CROQ_ERR_SHAPE;
+  if (M == 0 || N == 0) return CROQ_ERR_SHAPE;
+  if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (sched_tile_m <= 0 || sched_tile_n <= 0) return CROQ_ERR_SHAPE;
+  if (has_m) {
+    if (schedule_m->dims[0] != schedule_n->dims[0]) return CROQ_ERR_SHAPE;
+    const size_t tiles = ((M + sched_tile_m - 1) / sched_tile_m) * ((N + sched_tile_n - 1) / sched_tile_n);
+    if (schedule_m->dims[0] < tiles) return CROQ_ERR_SHAPE;
+  }
+  if (!aligned16(lhs->ptr) || !aligned16(rhs->ptr)) return CROQ_ERR_ALIGN;
+  if (K != 0 && (K * 2) % 16 != 0) return CROQ_ERR_ALIGN;  // TMA row pitch
+  if ((reinterpret_cast<uintptr_t>(output->ptr) & 1u) != 0) return CROQ_ERR_ALIGN;
+  return CROQ_OK;
+}
+
+template <bool kBf16>
+int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                 const croq_view1* schedule_m, const croq_view1* schedule_n, int sched_tile_m,
+                 int sched_tile_n, croq_stream stream_) {
+  int rc = check_dense_views(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m, sched_tile_n);
+  if (rc != CROQ_OK) return rc;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int M = static_cast<int>(lhs->dims[0]);
+  const int K = static_cast<int>(lhs->dims[1]);
+  const int N = static_cast<int>(rhs->dims[0]);
+  if (K == 0) {
+    CROQ_CUDA_TRY(cudaMemsetAsync(output->ptr, 0, static_cast<size_t>(M) * N * 2, stream));
+    return CROQ_OK;
+  }
+  DenseParams p;
+  p.out = static_cast<uint16_t*>(output->ptr);
+  p.M = M; p.N = N; p.K = K;
+  p.sched_m = schedule_m ? static_cast<const int*>(schedule_m->ptr) : nullptr;
+  p.sched_n = schedule_n ? static_cast<const int*>(schedule_n->ptr) : nullptr;
+  p.tile_m = sched_tile_m;
+  p.tile_n = sched_tile_n;
+  p.tiles_m = (M + sched_tile_m - 1) / sched_tile_m;
+  p.tiles_n = (N + sched_tile_n - 1) / sched_tile_n;
+  p.sub_m = (sched_tile_m + kBlockM - 1) / kBlockM;
+  p.sub_n = (sched_tile_n + kBlockN - 1) / kBlockN;
+  const long long total = 1ll * p.tiles_m * p.tiles_n * p.sub_m * p.sub_n;
+  if (total > 0x7FFFFFFFll) return CROQ_ERR_SHAPE;
+  p.total_work = static_cast<int>(total);
+  p.status = st->status_dev;
+
+  const CUtensorMapDataType dt =
+      kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_a, map_b;
+  rc = encode_tensor_map_2d(&map_a, dt, 2, lhs->ptr, M, K, kBlockM, kBlockK);
+  if (rc != CROQ_OK) return rc;
+  rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, kBlockN, kBlockK);
+  if (rc != CROQ_OK) return rc;
+
+  auto kernel = gemm_dense_kernel<kBf16>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[kBf16 ? 1 : 0]) {
+    CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytes)));
+    attr_set[kBf16 ? 1 : 0] = true;
+  }
+  const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+}  // namespace
+
+}  // namespace croq
+
+extern "C" {
+
+int croq_matmul_f16(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                    const croq_view1* schedule_m, const croq_view1* schedule_n,
+                    int sched_tile_m, int sched_tile_n, croq_stream stream) {
+  return croq::launch_dense<false>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
+                                   sched_tile_n, stream);
+}
+
+int croq_matmul_bf16(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                     const croq_view1* schedule_m, const croq_view1* schedule_n,
+                     int sched_tile_m, int sched_tile_n, croq_stream stream) {
+  return croq::launch_dense<true>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
+                                  sched_tile_n, stream);
+}
+
+}  // extern "C"

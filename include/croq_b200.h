@@ -1,0 +1,162 @@
+/* libcroq_b200 — C ABI of the B200 (sm_100a) GEMM family.
+ *
+ * Each entry point stands in for the host wrapper that the reference compiler
+ * emits for one `__co__` function (emission: lib/Target/GPU/cute_codegen.cpp:
+ * 2294-2421 prologue, 9896-9984 shape checks, 10051-10283 TMA descriptors,
+ * 3590-3754 launch). Arguments keep the reference order and meaning; tensors
+ * are passed as views whose memory layout equals choreo::spanned_view<T,Rank>
+ * (runtime/choreo.h:758-762): a data pointer followed by Rank size_t extents,
+ * dense row-major, last dimension contiguous.
+ *
+ * Differences from the reference wrapper, on purpose:
+ *  - every entry returns an int status (0 = ok) instead of aborting
+ *    (runtime/choreo.h:243-257 aborts);
+ *  - every entry takes a stream and does not block; croq_synchronize() blocks
+ *    like the reference's trailing cudaDeviceSynchronize and also reports
+ *    device-side conditions (a wait that ran out, a bad schedule entry);
+ *  - all pointers are DEVICE pointers (the `global` parameters of the
+ *    reference, Documents/Documentation/io-and-linking.md:19-47).
+ */
+#ifndef CROQ_B200_H_
+#define CROQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same layout as choreo::spanned_view<T,1|2|3>. */
+typedef struct { void* ptr; size_t dims[1]; } croq_view1;
+typedef struct { void* ptr; size_t dims[2]; } croq_view2;
+typedef struct { void* ptr; size_t dims[3]; } croq_view3;
+
+/* cudaStream_t without pulling in the CUDA headers. */
+typedef void* croq_stream;
+
+enum {
+  CROQ_OK = 0,
+  CROQ_ERR_NULL = 1,         /* null view or null data pointer */
+  CROQ_ERR_SHAPE = 2,        /* extents disagree (the reference's runtime_check) */
+  CROQ_ERR_ALIGN = 3,        /* base or row pitch not 16-byte aligned (TMA) */
+  CROQ_ERR_CUDA = 4,         /* a CUDA call failed; see croq_last_error_string */
+  CROQ_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out */
+  CROQ_ERR_SCHEDULE = 6,     /* schedule_m / schedule_n entry outside the tile grid */
+  CROQ_ERR_INDEX = 7,        /* routing / permutation index out of range */
+  CROQ_ERR_UNSUPPORTED = 8,  /* argument combination this build does not cover */
+  CROQ_ERR_NO_DEVICE = 9     /* no sm_100 device is current */
+};
+
+enum { CROQ_DTYPE_F16 = 0, CROQ_DTYPE_BF16 = 1 };
+
+const char* croq_status_string(int status);
+/* Text of the last CUDA error seen by the calling thread ("" if none). */
+const char* croq_last_error_string(void);
+/* Library version, "major.minor.patch". */
+const char* croq_version(void);
+
+/* Blocks until `stream` is idle (NULL = legacy default stream), then returns
+ * and clears the status kernels reported since the last call on this device:
+ * CROQ_OK, CROQ_ERR_TIMEOUT, CROQ_ERR_SCHEDULE or CROQ_ERR_INDEX. Mirrors the
+ * cudaDeviceSynchronize / cudaStreamSynchronize that ends every reference
+ * wrapper (cute_codegen.cpp:3748-3754). */
+int croq_synchronize(croq_stream stream);
+
+/* Persistent GEMM with a caller-supplied tile schedule.
+ * Replaces `__co__ matmul_persis_hilbert_sm90(lhs, rhs, output, schedule_m,
+ * schedule_n)` (tests/gpu/end2end/wgmma_persis.co:5-33; README.md:82-107):
+ *   output[m,n] = RN( sum_k lhs[m,k] * rhs[n,k] ), fp32 accumulation.
+ * lhs [M,K], rhs [N,K], output [M,N], 16-bit elements of `dtype`.
+ * schedule_m / schedule_n: s32 [T]; entry i names the (row, column) index of
+ * the i-th schedule tile, a tile being sched_tile_m x sched_tile_n outputs;
+ * T >= cdiv(M,sched_tile_m) * cdiv(N,sched_tile_n) and the first that many
+ * entries are visited in order (tile_id = iteration * #CTAs + cta, as in the
+ * reference). Both schedule views may be NULL: tiles are then visited
+ * row-major like `matmul_f16_ws_1p3c_persis` (wgmma_persis.co:35-92). */
+int croq_matmul_f16(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                    const croq_view1* schedule_m, const croq_view1* schedule_n,
+                    int sched_tile_m, int sched_tile_n, croq_stream stream);
+int croq_matmul_bf16(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                     const croq_view1* schedule_m, const croq_view1* schedule_n,
+                     int sched_tile_m, int sched_tile_n, croq_stream stream);
+
+/* FP8 e4m3 GEMM with fp32 block scales.
+ * Replaces `__co__ blockscale_gemm_e4m3_ws_persis(lhs, scale_lhs, rhs,
+ * scale_rhs, output)` (wgmma_persis.co:94-154) in its fp32-accumulator form
+ * (runtime/choreo_cute.h:3851-3860):
+ *   acc = 0; for each 128-wide K block kb:
+ *     P   = sum_{k in kb} lhs[m,k] * rhs[n,k]            (fp32)
+ *     acc = fma(P, scale_lhs[m,kb] * scale_rhs[n/128,kb], acc)
+ *   output[m,n] = RN(acc)
+ * lhs e4m3 [M,K], scale_lhs f32 [M, cdiv(K,128)], rhs e4m3 [N,K],
+ * scale_rhs f32 [cdiv(N,128), cdiv(K,128)], output [M,N] of out_dtype. */
+int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2* scale_lhs,
+                              const croq_view2* rhs, const croq_view2* scale_rhs,
+                              const croq_view2* output, int out_dtype, croq_stream stream);
+
+/* 2:4 structured-sparse f16 GEMM.
+ * Replaces the sparse `__co__` kernels of tests/gpu/end2end/gemm_sp.co:101-290:
+ *   output = dense(lhs_packed, lhs_meta) * rhs^T, fp32 accumulation.
+ * lhs_packed f16 [M, K/2]; lhs_meta u8 [M, K/8] in the reference's host
+ * encoding (runtime/choreo.h:1539-1571: one nibble per group of four K
+ * positions, idx0 | idx1<<2 with idx0 < idx1, even group in the low nibble);
+ * rhs f16 [N,K]; output [M,N] of out_dtype. */
+int croq_gemm_sp_f16(const croq_view2* lhs_packed, const croq_view2* lhs_meta,
+                     const croq_view2* rhs, const croq_view2* output, int out_dtype,
+                     croq_stream stream);
+
+/* ---- MoE path. The reference has no counterpart for these entry points; the
+ * argument conventions follow the spanned-view rules above. ---- */
+
+/* Top-k routing and the stable token permutation.
+ * logits f32 [T,E]; topk_idx s32 [T,k] (k largest raw logits per token,
+ * ordered by logit descending then expert ascending); topk_w f32 [T,k]
+ * (softmax over all E, renormalised over the k selected when norm_topk != 0);
+ * expert_counts s32 [E]; expert_offsets s32 [E+1] (exclusive prefix sum);
+ * perm_to_src s32 [T*k] and src_to_perm s32 [T*k]: expanded row r = t*k+j is
+ * placed at position src_to_perm[r]; within one expert rows keep ascending r. */
+int croq_moe_route_topk(const croq_view2* logits, int k, int norm_topk,
+                        const croq_view2* topk_idx, const croq_view2* topk_w,
+                        const croq_view1* expert_counts, const croq_view1* expert_offsets,
+                        const croq_view1* perm_to_src, const croq_view1* src_to_perm,
+                        croq_stream stream);
+
+/* Gather rows into expert order: dst[pos,:] = src[perm_to_src[pos] / k, :].
+ * src bf16 [T,H]; dst bf16 [T*k,H]. */
+int croq_moe_permute(const croq_view2* src, const croq_view1* perm_to_src, int k,
+                     const croq_view2* dst, croq_stream stream);
+
+/* Same gather fused with the activation quantiser: dst_q e4m3 [T*k,H] and
+ * dst_scale f32 [T*k, H/128] with scale = amax/448 per 1x128 block (1 when the
+ * block is all zero) and q = RN_e4m3(x / scale). */
+int croq_moe_permute_quant_e4m3(const croq_view2* src, const croq_view1* perm_to_src, int k,
+                                const croq_view2* dst_q, const croq_view2* dst_scale,
+                                croq_stream stream);
+
+/* Weighted combine: out[t,:] = RN_bf16( sum_j topk_w[t,j] * y[src_to_perm[t*k+j], :] ),
+ * summed in ascending j in fp32. y bf16 [T*k,H]; out bf16 [T,H]. */
+int croq_moe_unpermute(const croq_view2* y, const croq_view1* src_to_perm,
+                       const croq_view2* topk_w, const croq_view2* out, croq_stream stream);
+
+/* Grouped block-scaled FP8 GEMM over expert-sorted rows:
+ *   for each expert e and row r in [expert_offsets[e], expert_offsets[e+1]):
+ *     out[r,:] = blockscale_gemm(x[r,:], x_scale[r,:], w[e], w_scale[e])
+ * x e4m3 [R,K]; x_scale f32 [R, K/128]; w e4m3 [E,N,K]; w_scale f32
+ * [E, cdiv(N,128), K/128]; expert_offsets s32 [E+1] (device); out bf16 [R,N].
+ * When swiglu != 0, N must be even and out is [R, N/2] with
+ *   out[r,c] = RN_bf16( silu(h[r,c]) * h[r, N/2 + c] ), h the fp32 GEMM result. */
+int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
+                               const croq_view3* w, const croq_view3* w_scale,
+                               const croq_view1* expert_offsets, const croq_view2* out,
+                               int swiglu, croq_stream stream);
+
+/* Row-wise activation quantiser used between the two expert GEMMs:
+ * q e4m3 [R,H], scale f32 [R, H/128] from x bf16 [R,H] (rule as above). */
+int croq_quant_rows_e4m3(const croq_view2* x, const croq_view2* q, const croq_view2* scale,
+                         croq_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CROQ_B200_H_ */
