@@ -2,10 +2,6 @@
 #include "croq_host.h"
 
 extern "C" {
-int croq_blockscale_gemm_e4m3(const croq_view2*, const croq_view2*, const croq_view2*,
-                              const croq_view2*, const croq_view2*, int, croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
 int croq_gemm_sp_f16(const croq_view2*, const croq_view2*, const croq_view2*, const croq_view2*,
                      int, croq_stream) {
   return CROQ_ERR_UNSUPPORTED;
