@@ -1,0 +1,276 @@
+"""numpy front end of the CPU oracle — TEST INFRASTRUCTURE ONLY.
+
+Loads ``oracle/libcroq_oracle.so`` (built from ``croq_oracle.c``; see the
+header of that file for which parts are pinned against the reference and which
+are "parity unpinned") and, when present, the two libraries under
+``oracle/_ref`` that are compiled from the reference's own sources and from
+CUDA's host-side conversions. Only ``tests/``, ``__graft_entry__.smoke()`` and
+the CPU-baseline legs of ``bench.py`` import this module; the shipped package
+``croqtile_b200`` never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from ctypes import POINTER, c_float, c_int, c_int32, c_size_t, c_uint, c_uint8, c_uint16, c_void_p
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "libcroq_oracle.so"
+REF_LIB = HERE / "_ref" / "libchoreo_ref.so"
+CODEC_LIB = HERE / "_ref" / "libcuda_codecs.so"
+
+
+def build(ref: bool = False) -> None:
+    """Compiles the C oracle (and with ``ref`` the reference-derived libraries)."""
+    subprocess.run(["make", "-C", str(HERE), "--no-print-directory"], check=True)
+    if ref:
+        subprocess.run(["make", "-C", str(HERE), "--no-print-directory", "ref"], check=True)
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB.exists():
+            build()
+        _lib = ctypes.CDLL(str(LIB))
+    return _lib
+
+
+def ref_lib():
+    """Library compiled from the reference's sources, or None when absent."""
+    return ctypes.CDLL(str(REF_LIB)) if REF_LIB.exists() else None
+
+
+def codec_lib():
+    """CUDA's host conversions, or None when absent."""
+    return ctypes.CDLL(str(CODEC_LIB)) if CODEC_LIB.exists() else None
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(c_void_p)
+
+
+def _c(a, dtype) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+# ------------------------------------------------------------------ codecs --
+
+def _convert(fn_name: str, src: np.ndarray, src_t, dst_t, library=None) -> np.ndarray:
+    src = _c(src, src_t)
+    dst = np.empty(src.shape, dst_t)
+    fn = getattr(library or lib(), fn_name)
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_size_t]
+    fn(_p(src), _p(dst), src.size)
+    return dst
+
+
+def f32_to_bf16(x): return _convert("oracle_f32_to_bf16_n", x, np.float32, np.uint16)
+def f32_to_f16(x): return _convert("oracle_f32_to_f16_n", x, np.float32, np.uint16)
+def f32_to_e4m3(x): return _convert("oracle_f32_to_e4m3_n", x, np.float32, np.uint8)
+def bf16_to_f32(x): return _convert("oracle_bf16_to_f32_n", x, np.uint16, np.float32)
+def f16_to_f32(x): return _convert("oracle_f16_to_f32_n", x, np.uint16, np.float32)
+def e4m3_to_f32(x): return _convert("oracle_e4m3_to_f32_n", x, np.uint8, np.float32)
+
+
+def round_to(x: np.ndarray, dtype: str) -> np.ndarray:
+    """fp32 -> bit pattern of 'f16' | 'bf16'."""
+    return {"f16": f32_to_f16, "bf16": f32_to_bf16}[dtype](x)
+
+
+def decode(bits: np.ndarray, dtype: str) -> np.ndarray:
+    """bit pattern of 'f16' | 'bf16' | 'e4m3' -> fp32."""
+    return {"f16": f16_to_f32, "bf16": bf16_to_f32, "e4m3": e4m3_to_f32}[dtype](bits)
+
+
+# -------------------------------------------------------------------- GEMMs --
+
+def gemm_row_row(lhs_f32, rhs_f32, tile=(128, 256, 64), schedule_m=None, schedule_n=None,
+                 tile_range=None) -> np.ndarray:
+    """fp32 out[M,N] = lhs[M,K] @ rhs[N,K]^T with the reference CPU loop
+    (k ascending, fp32), tiles visited in schedule order."""
+    lhs = _c(lhs_f32, np.float32)
+    rhs = _c(rhs_f32, np.float32)
+    M, K = lhs.shape
+    N = rhs.shape[0]
+    tm, tn, tk = tile
+    tiles = -(-M // tm) * -(-N // tn)
+    out = np.zeros((M, N), np.float32)
+    sm = _c(schedule_m, np.int32) if schedule_m is not None else None
+    sn = _c(schedule_n, np.int32) if schedule_n is not None else None
+    t0, t1 = tile_range if tile_range is not None else (0, tiles)
+    fn = lib().oracle_gemm_row_row
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_void_p, c_void_p, c_int, c_int]
+    fn(_p(lhs), _p(rhs), _p(out), M, N, K, tm, tn, tk,
+       _p(sm) if sm is not None else None, _p(sn) if sn is not None else None, t0, t1)
+    return out
+
+
+def blockscale_gemm_e4m3(lhs_u8, scale_lhs, rhs_u8, scale_rhs, rows=None) -> np.ndarray:
+    """fp32 result of the block-scaled GEMM on e4m3 bytes (rows = (begin, end)
+    restricts the computed output rows; the others stay zero)."""
+    lhs = _c(lhs_u8, np.uint8)
+    rhs = _c(rhs_u8, np.uint8)
+    sa = _c(scale_lhs, np.float32)
+    sb = _c(scale_rhs, np.float32)
+    M, K = lhs.shape
+    N = rhs.shape[0]
+    out = np.zeros((M, N), np.float32)
+    r0, r1 = rows if rows is not None else (0, M)
+    fn = lib().oracle_blockscale_gemm_e4m3
+    fn.restype = None
+    fn.argtypes = [c_void_p] * 5 + [c_int] * 5
+    fn(_p(lhs), _p(sa), _p(rhs), _p(sb), _p(out), M, N, K, r0, r1)
+    return out
+
+
+# ------------------------------------------------------------------- sparse --
+
+def sparse24_encode(dense_bits: np.ndarray):
+    """(packed u16 [M,K/2], meta u8 [M,K/8]) from dense 16-bit patterns [M,K]."""
+    d = _c(dense_bits, np.uint16)
+    M, K = d.shape
+    assert K % 8 == 0
+    packed = np.zeros((M, K // 2), np.uint16)
+    meta = np.zeros((M, K // 8), np.uint8)
+    fn = lib().oracle_sparse24_encode_u16
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int]
+    fn(_p(d), _p(packed), _p(meta), M, K)
+    return packed, meta
+
+
+def sparse24_decode(packed_bits: np.ndarray, meta: np.ndarray) -> np.ndarray:
+    p = _c(packed_bits, np.uint16)
+    m = _c(meta, np.uint8)
+    M, K2 = p.shape
+    K = K2 * 2
+    dense = np.zeros((M, K), np.uint16)
+    fn = lib().oracle_sparse24_decode_u16
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int]
+    fn(_p(p), _p(m), _p(dense), M, K)
+    return dense
+
+
+# ----------------------------------------------------------------- schedule --
+
+def hilbert_schedule(tiles_m: int, tiles_n: int):
+    size = 1
+    while size < max(tiles_m, tiles_n, 1):
+        size *= 2
+    sm = np.zeros(size * size, np.int32)
+    sn = np.zeros(size * size, np.int32)
+    fn = lib().oracle_hilbert_schedule
+    fn.restype = c_int
+    fn.argtypes = [c_int, c_int, c_void_p, c_void_p]
+    n = fn(tiles_m, tiles_n, _p(sm), _p(sn))
+    return sm[:n].copy(), sn[:n].copy()
+
+
+def sample_positions(M: int, N: int, num_samples: int) -> np.ndarray:
+    """Flat output indices the reference's sampled verifier inspects."""
+    out = np.zeros(num_samples, np.uint64)
+    fn = lib().oracle_sample_positions
+    fn.restype = c_size_t
+    fn.argtypes = [c_size_t, c_size_t, c_size_t, c_void_p]
+    n = fn(M, N, num_samples, _p(out))
+    return out[:n].astype(np.int64)
+
+
+# ---------------------------------------------------------------------- MoE --
+
+def moe_route_topk(logits, k: int, norm_topk: bool = True):
+    l = _c(logits, np.float32)
+    T, E = l.shape
+    idx = np.zeros((T, k), np.int32)
+    w = np.zeros((T, k), np.float32)
+    counts = np.zeros(E, np.int32)
+    offsets = np.zeros(E + 1, np.int32)
+    p2s = np.zeros(T * k, np.int32)
+    s2p = np.zeros(T * k, np.int32)
+    fn = lib().oracle_moe_route_topk
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 6
+    fn(_p(l), T, E, k, int(norm_topk), _p(idx), _p(w), _p(counts), _p(offsets), _p(p2s), _p(s2p))
+    return dict(topk_idx=idx, topk_w=w, expert_counts=counts, expert_offsets=offsets,
+                perm_to_src=p2s, src_to_perm=s2p)
+
+
+def quant_rows_e4m3(x_f32):
+    x = _c(x_f32, np.float32)
+    R, H = x.shape
+    q = np.zeros((R, H), np.uint8)
+    s = np.zeros((R, -(-H // 128)), np.float32)
+    fn = lib().oracle_quant_rows_e4m3_f32
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int]
+    fn(_p(x), _p(q), _p(s), R, H)
+    return q, s
+
+
+def quant_blocks_e4m3(w_f32):
+    """Weight quantiser of the benchmark recipe: 128x128 blocks, scale =
+    amax/448 (1 for an all-zero block), q = RN_e4m3(w / scale)."""
+    w = np.asarray(w_f32, np.float32)
+    N, K = w.shape[-2:]
+    lead = w.shape[:-2]
+    NB, KB = -(-N // 128), -(-K // 128)
+    wp = np.zeros(lead + (NB * 128, KB * 128), np.float32)
+    wp[..., :N, :K] = w
+    blk = wp.reshape(lead + (NB, 128, KB, 128))
+    amax = np.abs(blk).max(axis=(-3, -1))
+    scale = np.where(amax > 0, amax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+    scaled = (blk / scale[..., :, None, :, None]).reshape(lead + (NB * 128, KB * 128))[..., :N, :K]
+    return f32_to_e4m3(np.ascontiguousarray(scaled)), scale
+
+
+def moe_permute(src_bits, perm_to_src, k: int) -> np.ndarray:
+    s = _c(src_bits, np.uint16)
+    p = _c(perm_to_src, np.int32)
+    H = s.shape[1]
+    dst = np.zeros((p.size, H), np.uint16)
+    fn = lib().oracle_moe_permute_u16
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int]
+    fn(_p(s), _p(p), k, _p(dst), p.size, H)
+    return dst
+
+
+def moe_unpermute(y_bits, src_to_perm, topk_w) -> np.ndarray:
+    y = _c(y_bits, np.uint16)
+    s2p = _c(src_to_perm, np.int32)
+    w = _c(topk_w, np.float32)
+    T, k = w.shape
+    H = y.shape[1]
+    out = np.zeros((T, H), np.uint16)
+    fn = lib().oracle_moe_unpermute_bf16
+    fn.restype = None
+    fn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
+    fn(_p(y), _p(s2p), _p(w), _p(out), T, k, H)
+    return out
+
+
+def moe_grouped_gemm_e4m3(x_u8, x_scale, w_u8, w_scale, offsets, swiglu: bool) -> np.ndarray:
+    x = _c(x_u8, np.uint8)
+    xs = _c(x_scale, np.float32)
+    w = _c(w_u8, np.uint8)
+    ws = _c(w_scale, np.float32)
+    off = _c(offsets, np.int32)
+    E, N, K = w.shape
+    R = x.shape[0]
+    out = np.zeros((R, N // 2 if swiglu else N), np.uint16)
+    fn = lib().oracle_moe_grouped_gemm_e4m3
+    fn.restype = None
+    fn.argtypes = [c_void_p] * 5 + [c_int] * 4 + [c_void_p]
+    fn(_p(x), _p(xs), _p(w), _p(ws), _p(off), E, N, K, int(swiglu), _p(out))
+    return out
