@@ -46,6 +46,8 @@ int record_cuda_error(cudaError_t err, const char* what) {
   return CROQ_ERR_CUDA;
 }
 
+void clear_error() { g_error_text[0] = '\0'; }
+
 int record_text_error(int status, const char* what) {
   snprintf(g_error_text, sizeof(g_error_text), "%s", what);
   return status;
@@ -180,6 +182,7 @@ const char* croq_last_error_string(void) { return croq::g_error_text; }
 const char* croq_version(void) { return "0.1.0"; }
 
 int croq_synchronize(croq_stream stream) {
+  croq::clear_error();
   int rc = CROQ_OK;
   croq::DeviceState* st = croq::device_state(&rc);
   if (st == nullptr) return rc;

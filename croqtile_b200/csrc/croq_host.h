@@ -35,9 +35,20 @@ int record_text_error(int status, const char* what);
     if (croq_err__ != cudaSuccess) return ::croq::record_cuda_error(croq_err__, #expr); \
   } while (0)
 
-inline bool view_ok(const croq_view1* v) { return v != nullptr && v->ptr != nullptr; }
-inline bool view_ok(const croq_view2* v) { return v != nullptr && v->ptr != nullptr; }
-inline bool view_ok(const croq_view3* v) { return v != nullptr && v->ptr != nullptr; }
+// Forgets the calling thread's error text; every entry point starts with it.
+void clear_error();
+
+// A view is usable when it exists and has a data pointer; a view without any
+// element (some extent 0) may carry a null pointer.
+inline bool view_ok(const croq_view1* v) {
+  return v != nullptr && (v->ptr != nullptr || v->dims[0] == 0);
+}
+inline bool view_ok(const croq_view2* v) {
+  return v != nullptr && (v->ptr != nullptr || v->dims[0] * v->dims[1] == 0);
+}
+inline bool view_ok(const croq_view3* v) {
+  return v != nullptr && (v->ptr != nullptr || v->dims[0] * v->dims[1] * v->dims[2] == 0);
+}
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Encodes a 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements

@@ -320,6 +320,7 @@ extern "C" int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2
                                          const croq_view2* output, int out_dtype,
                                          croq_stream stream) {
   using namespace croq;
+  clear_error();
   if (!view_ok(lhs) || !view_ok(scale_lhs) || !view_ok(rhs) || !view_ok(scale_rhs) ||
       !view_ok(output))
     return CROQ_ERR_NULL;

@@ -220,7 +220,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_ld_wait();
         const int col0 = t.n0 + c * 32;
         if (row < t.m_end && col0 < t.n_end) {
-          if (vec_ok && col0 + 32 <= t.n_end) {
+          if (vec_ok && ((col0 & 7) == 0) && col0 + 32 <= t.n_end) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 pk;
@@ -282,6 +282,7 @@ template <bool kBf16>
 int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
                  const croq_view1* schedule_m, const croq_view1* schedule_n, int sched_tile_m,
                  int sched_tile_n, croq_stream stream_) {
+  clear_error();
   int rc = check_dense_views(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m, sched_tile_n);
   if (rc != CROQ_OK) return rc;
   DeviceState* st = device_state(&rc);

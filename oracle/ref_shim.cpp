@@ -12,6 +12,8 @@
 // (hilbert_rotate, hilbert_index_to_xy, build_hilbert_schedule), cut out at
 // build time into a temporary file that the recipe deletes again.
 #include <cstdint>
+#include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <random>
 
@@ -60,6 +62,55 @@ __attribute__((visibility("default"))) void ref_sparse_kat_inputs(
       float value = dist(gen);
       if (std::fabs(value) < 0.1f) value = (value < 0.0f ? -0.25f : 0.25f);
       rhs[(size_t)col * K + kk] = value;
+    }
+}
+
+// Block-scaled FP8 GEMM in the structure the reference's CPU target gives
+// `blockscale_gemm_e4m3_ws_persis` (tests/gpu/end2end/wgmma_persis.co:94-154):
+// sequential loops over 64x128 output tiles (cc_codegen.cpp:1046-1066), per
+// 128-wide K block the operands are staged (strided copy), the partial product
+// comes from the reference's own choreo::cc::mma_exec_row_row on a zeroed
+// scratch tile, and `mma.scale` adds partial * (sa[row] * sb) into the fp32
+// accumulators (operation order of runtime/choreo_cute.h:3812-3813,3851-3860;
+// the CPU target's own A-only scaling, cc_codegen.cpp:1267-1283, would drop
+// scale_rhs). Operands arrive as e4m3 bytes with a 256-entry decode table
+// (the CC target has no fp8 type: cc_codegen.cpp:36,55-61). Computes the tiles
+// [tile_m_begin, tile_m_end) x [tile_n_begin, tile_n_end) so that callers can
+// spread tiles over host threads or time a bounded sample.
+__attribute__((visibility("default"))) void ref_blockscale_gemm_e4m3(
+    const uint8_t* lhs, const float* scale_lhs, const uint8_t* rhs, const float* scale_rhs,
+    float* out, const float* decode_lut, int M, int N, int K, int tile_m_begin, int tile_m_end,
+    int tile_n_begin, int tile_n_end) {
+  constexpr int TM = 64, TN = 128, TK = 128;
+  const int KB = (K + TK - 1) / TK;
+  const int tiles_n = (N + TN - 1) / TN;
+  alignas(64) static thread_local float a_s[TM * TK];
+  alignas(64) static thread_local float b_s[TN * TK];
+  alignas(64) static thread_local float part[TM * TN];
+  alignas(64) static thread_local float zero[TM * TN];
+  alignas(64) static thread_local float acc[TM * TN];
+  std::memset(zero, 0, sizeof(zero));
+  for (int bm = tile_m_begin; bm < tile_m_end; ++bm)
+    for (int bn = tile_n_begin; bn < tile_n_end && bn < tiles_n; ++bn) {
+      const int m0 = bm * TM, n0 = bn * TN;
+      const int mm = std::min(TM, M - m0), nn = std::min(TN, N - n0);
+      if (mm <= 0 || nn <= 0) continue;
+      std::memset(acc, 0, sizeof(acc));
+      for (int kb = 0; kb < KB; ++kb) {
+        const int k0 = kb * TK, kk = std::min(TK, K - k0);
+        for (int i = 0; i < mm; ++i)
+          for (int k = 0; k < kk; ++k) a_s[i * kk + k] = decode_lut[lhs[(size_t)(m0 + i) * K + k0 + k]];
+        for (int j = 0; j < nn; ++j)
+          for (int k = 0; k < kk; ++k) b_s[j * kk + k] = decode_lut[rhs[(size_t)(n0 + j) * K + k0 + k]];
+        choreo::cc::mma_exec_row_row<float, float, float, float>(part, a_s, b_s, zero, mm, nn, kk);
+        const float sb = scale_rhs[(size_t)(n0 / 128) * KB + kb];
+        for (int i = 0; i < mm; ++i) {
+          const float s = scale_lhs[(size_t)(m0 + i) * KB + kb] * sb;
+          for (int j = 0; j < nn; ++j) acc[i * nn + j] = std::fmaf(part[i * nn + j], s, acc[i * nn + j]);
+        }
+      }
+      for (int i = 0; i < mm; ++i)
+        std::memcpy(out + (size_t)(m0 + i) * N + n0, acc + i * nn, sizeof(float) * nn);
     }
 }
 
