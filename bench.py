@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the libcroq_b200 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl croq|reference]
+                    [--workload NAME]
+
+Prints ONE JSON line. A step is one pass of the hot path over one batch of
+seeded synthetic input; the default workload is the FP8 e4m3 block-scaled GEMM
+at M=N=K=8192, the configuration the headline metric is quoted on. With N > 1
+(launched under torch.distributed.run, one rank per GPU) the right operand is
+sharded along N: every rank owns an [8192, K] slab of a [8192*N, K] operand
+and computes its own [M, 8192] output slab with no data-path collective, so
+per-GPU work is fixed (weak scaling); `value` is the work of all ranks over
+the slowest rank's device time.
+
+`--impl reference` times the reference's CPU formulation of the same
+workload on the host cores (oracle/_ref when it was built from the reference
+tree, else the oracle port), each step a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (kind, M, N, K)
+    "fp8_blockscale_8192": ("blockscale", 8192, 8192, 8192),
+    "fp8_blockscale_4096x7168x7168": ("blockscale", 4096, 7168, 7168),
+    "bf16_hilbert_8192": ("dense", 8192, 8192, 8192),
+}
+NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0}
+
+
+def load_peaks():
+    """(hbm GB/s, bf16 TFLOP/s burst, source text) from MEASURED_PEAKS.json or the fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# ----------------------------------------------------------------- clocks ---
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only)
+    while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------ CPU baseline ---
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+class CpuBlockscale:
+    """The reference's CPU formulation of the block-scaled GEMM on a sample of
+    output tiles, spread over host threads (ctypes releases the GIL)."""
+
+    def __init__(self, M, N, K, seed=3001):
+        import ctypes
+        from oracle import oracle as o
+        self.o, self.M, self.N, self.K = o, M, N, K
+        rng = np.random.default_rng(seed)
+        self.rows = min(M, 64 * host_cores())
+        a = rng.standard_normal((self.rows, K), dtype=np.float32)
+        self.a_q, self.sa = o.quant_rows_e4m3(a)
+        b = rng.standard_normal((N, K), dtype=np.float32)
+        self.b_q, self.sb = o.quant_blocks_e4m3(b)
+        self.lut = o.e4m3_to_f32(np.arange(256, dtype=np.uint8))
+        self.out = np.zeros((self.rows, N), np.float32)
+        self.ref = o.ref_lib()
+        self.kind = "reference" if self.ref is not None else "port"
+        if self.ref is not None:
+            f = self.ref.ref_blockscale_gemm_e4m3
+            f.restype = None
+            f.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 7
+            self.fn = f
+        self.threads = max(1, min(host_cores(), self.rows // 64))
+
+    def _ptr(self, a):
+        import ctypes
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    def run(self, tiles_per_thread: int) -> float:
+        """One step: every thread computes `tiles_per_thread` 64x128 output tiles
+        over the full K. Returns the flop count of the step."""
+        tiles_n = self.N // 128
+        tiles_per_thread = max(1, min(tiles_per_thread, tiles_n))
+
+        def work(t):
+            if self.ref is not None:
+                self.fn(self._ptr(self.a_q), self._ptr(self.sa), self._ptr(self.b_q), self._ptr(self.sb),
+                        self._ptr(self.out), self._ptr(self.lut), self.rows, self.N, self.K,
+                        t, t + 1, 0, tiles_per_thread)
+            else:
+                rows = max(1, tiles_per_thread * 128 * 64 // self.N)
+                self.o.blockscale_gemm_e4m3(self.a_q[t * 64:t * 64 + rows], self.sa[t * 64:t * 64 + rows],
+                                            self.b_q, self.sb)
+        with ThreadPoolExecutor(self.threads) as pool:
+            list(pool.map(work, range(self.threads)))
+        if self.ref is not None:
+            outputs = self.threads * tiles_per_thread * 64 * 128
+        else:
+            outputs = self.threads * max(1, tiles_per_thread * 128 * 64 // self.N) * self.N
+        return 2.0 * outputs * self.K
+
+    def sample_text(self, tiles_per_thread: int) -> str:
+        return (f"{self.threads} threads x {tiles_per_thread} output tiles of 64x128 over K={self.K} "
+                f"per step ({self.kind} CPU formulation of the same GEMM)")
+
+
+def cpu_baseline_line(kind, M, N, K, budget_s: float = 12.0):
+    """Times the CPU formulation on a bounded sample; returns the cpu_baseline object."""
+    if kind != "blockscale":
+        from oracle import oracle as o
+        rng = np.random.default_rng(2001)
+        rows = 64
+        a = o.bf16_to_f32(o.f32_to_bf16(rng.standard_normal((rows, K), dtype=np.float32)))
+        b = o.bf16_to_f32(o.f32_to_bf16(rng.standard_normal((1024, K), dtype=np.float32)))
+        t0 = time.perf_counter()
+        o.gemm_row_row(a, b, tile=(64, 128, 64))
+        dt = time.perf_counter() - t0
+        return {"value": 2.0 * rows * 1024 * K / dt / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                "sample": f"{rows}x1024 outputs over K={K}, oracle port of choreo::cc::mma_exec_row_row tile loops"}
+    cpu = CpuBlockscale(M, N, K)
+    t0 = time.perf_counter()
+    flops = cpu.run(1)
+    probe = time.perf_counter() - t0
+    tiles = max(1, int(budget_s / max(probe, 1e-3)))
+    t0 = time.perf_counter()
+    flops = cpu.run(tiles)
+    dt = time.perf_counter() - t0
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cpu.threads, "kind": cpu.kind,
+            "sample": cpu.sample_text(min(tiles, N // 128))}
+
+
+def run_reference_arm(args, kind, M, N, K):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if kind != "blockscale":
+        base = cpu_baseline_line(kind, M, N, K)
+        value, cores, sample, ckind, ms = base["value"], base["cores"], base["sample"], base["kind"], None
+    else:
+        cpu = CpuBlockscale(M, N, K)
+        t0 = time.perf_counter()
+        cpu.run(1)
+        probe = time.perf_counter() - t0
+        budget = 100.0 / max(1, args.steps + args.warmup)
+        tiles = max(1, min(N // 128, int(budget / max(probe, 1e-3))))
+        for _ in range(args.warmup):
+            cpu.run(tiles)
+        t0 = time.perf_counter()
+        flops = 0.0
+        for _ in range(args.steps):
+            flops += cpu.run(tiles)
+        dt = time.perf_counter() - t0
+        value, cores, sample, ckind = flops / dt / 1e12, cpu.threads, cpu.sample_text(tiles), cpu.kind
+        ms = dt / args.steps * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC[kind], "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "e4m3" if kind == "blockscale" else "bf16", "data": "synthetic",
+        "config": config_of(args, kind, M, N, K),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": ckind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+METRIC = {
+    "blockscale": "FP8 block-scaled GEMM TFLOP/s & % B200 peak",
+    "dense": "persistent bf16 GEMM TFLOP/s & % B200 peak",
+}
+
+
+def config_of(args, kind, M, N, K):
+    return {
+        "workload": args.workload,
+        "M": M, "N_per_gpu": N, "N_global": N * args.gpus, "K": K,
+        "inputs": ("A e4m3 [M,K] + f32 scales per 1x128, B e4m3 [N,K] + f32 scales per 128x128, out bf16; "
+                   "N(0,1) sources quantised x*448/amax" if kind == "blockscale"
+                   else "lhs/rhs bf16 N(0,1)/sqrt(K), Hilbert schedule over 256x256 tiles, out bf16"),
+        "sharding": "right operand and output sharded along N, no collective" if args.gpus > 1 else "single GPU",
+        "l2": "two operand/output sets (>= 256 MiB each) used alternately; each exceeds the 126 MB L2",
+    }
+
+
+# --------------------------------------------------------------- GPU arm ---
+
+def run_croq_arm(args, kind, M, N, K):
+    import torch
+    import torch.distributed as dist
+    from croqtile_b200 import api, hilbert_schedule
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def make_set(seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        if kind == "blockscale":
+            a = torch.randn((M, K), generator=g, device=dev)
+            amax = a.view(M, K // 128, 128).abs().amax(-1)
+            sa = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax)).contiguous()
+            aq = (a.view(M, K // 128, 128) / sa[..., None]).view(M, K).to(torch.float8_e4m3fn)
+            del a
+            g.manual_seed(seed + 1 + 1000 * rank)       # every rank owns a different N slab
+            b = torch.randn((N, K), generator=g, device=dev)
+            bmax = b.view(N // 128, 128, K // 128, 128).abs().amax((1, 3))
+            sb = torch.where(bmax > 0, bmax / 448.0, torch.ones_like(bmax)).contiguous()
+            bq = (b.view(N // 128, 128, K // 128, 128) / sb[:, None, :, None]).view(N, K).to(torch.float8_e4m3fn)
+            del b
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            return dict(args=(aq, sa, bq, sb), out=out)
+        a = (torch.randn((M, K), generator=g, device=dev) / K ** 0.5).to(torch.bfloat16)
+        g.manual_seed(seed + 1 + 1000 * rank)
+        b = (torch.randn((N, K), generator=g, device=dev) / K ** 0.5).to(torch.bfloat16)
+        sm, sn = hilbert_schedule(-(-M // 256), -(-N // 256))
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        return dict(args=(a, b), out=out, sched=(torch.from_numpy(sm).to(dev), torch.from_numpy(sn).to(dev)))
+
+    sets = [make_set(3001), make_set(4001)]
+
+    def step(i):
+        s = sets[i & 1]
+        if kind == "blockscale":
+            api.blockscale_gemm_e4m3(*s["args"], s["out"])
+        else:
+            api.matmul(*s["args"], s["out"], s["sched"][0], s["sched"][1], 256, 256)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    api.synchronize()
+    barrier()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local) as clocks:
+        events[0].record()
+        for i in range(args.steps):
+            step(i)
+            events[i + 1].record()
+        torch.cuda.synchronize()
+    barrier()
+    api.synchronize()   # raises if any kernel reported a device-side fault
+    total_ms = events[0].elapsed_time(events[-1])
+    per_step = np.array([events[i].elapsed_time(events[i + 1]) for i in range(args.steps)])
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max = float(t.item())
+
+    flops_step_rank = 2.0 * M * N * K
+    value = flops_step_rank * world * args.steps / (total_ms_max * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers in, result back to the host, every step ----
+    s = sets[0]
+    host_in = [x.cpu().pin_memory() for x in s["args"]]
+    dev_in = [torch.empty_like(x) for x in s["args"]]
+    host_out = torch.empty(s["out"].shape, dtype=s["out"].dtype).pin_memory()
+    h2d = sum(x.numel() * x.element_size() for x in host_in)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        for h, d in zip(host_in, dev_in):
+            d.copy_(h, non_blocking=True)
+        if kind == "blockscale":
+            api.blockscale_gemm_e4m3(*dev_in, s["out"])
+        else:
+            api.matmul(*dev_in, s["out"], s["sched"][0], s["sched"][1], 256, 256)
+        host_out.copy_(s["out"], non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 8))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step_rank * world * e2e_steps / (float(te.item()) * 1e-3) / 1e12
+    api.synchronize()
+
+    if rank == 0:
+        hbm, bf16_peak, src = load_peaks()
+        # No FP8 figure is measured on this pool; the fp8 tensor rate is twice
+        # the bf16 rate, so the fp8 roofline uses 2x the measured bf16 burst.
+        peak = bf16_peak * (2.0 if kind == "blockscale" else 1.0)
+        launch_ms = float(per_step.mean())
+        achieved = flops_step_rank / (launch_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC[kind], "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms_max / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3" if kind == "blockscale" else "bf16", "data": "synthetic",
+            "config": config_of(args, kind, M, N, K),
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": (f"of {src}: " + ("2 x " if kind == "blockscale" else "") +
+                                f"bf16 cuBLAS burst {bf16_peak} TFLOP/s"),
+                "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[kind],
+                "nominal_peak": NOMINAL_PEAK_TFLOPS[kind],
+                "kernel": "gemm_blockscale_kernel" if kind == "blockscale" else "gemm_dense_kernel",
+                "launch_ms_mean": launch_ms, "launch_ms_min": float(per_step.min()),
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_line(kind, M, N, K)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="croq", choices=["croq", "reference"])
+    ap.add_argument("--workload", default="fp8_blockscale_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    kind, M, N, K = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, kind, M, N, K)
+    else:
+        run_croq_arm(args, kind, M, N, K)
+
+
+if __name__ == "__main__":
+    main()
