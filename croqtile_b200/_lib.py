@@ -44,6 +44,7 @@ SIGNATURES = {
     "croq_last_error_string": (c_char_p, []),
     "croq_version": (c_char_p, []),
     "croq_synchronize": (c_int, [c_void_p]),
+    "croq_last_kernel_clock": (c_int, [POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "croq_matmul_f16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
     "croq_matmul_bf16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
     "croq_blockscale_gemm_e4m3": (c_int, [P2, P2, P2, P2, P2, c_int, c_void_p]),

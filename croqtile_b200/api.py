@@ -61,6 +61,15 @@ def synchronize() -> None:
     _lib.check(lib.croq_synchronize(_stream()), "croq_synchronize")
 
 
+def last_kernel_clock() -> tuple[float, float]:
+    """(SM MHz, duration in us) the last GEMM kernel measured on itself; call
+    after ``synchronize()``."""
+    lib = _lib.load()
+    mhz, us = ctypes.c_double(), ctypes.c_double()
+    _lib.check(lib.croq_last_kernel_clock(ctypes.byref(mhz), ctypes.byref(us)), "croq_last_kernel_clock")
+    return mhz.value, us.value
+
+
 def matmul(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor | None = None,
            schedule_m: torch.Tensor | None = None, schedule_n: torch.Tensor | None = None,
            sched_tile_m: int = 256, sched_tile_n: int = 256) -> torch.Tensor:

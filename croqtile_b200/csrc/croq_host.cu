@@ -181,6 +181,20 @@ const char* croq_last_error_string(void) { return croq::g_error_text; }
 
 const char* croq_version(void) { return "0.1.0"; }
 
+int croq_last_kernel_clock(double* sm_mhz, double* kernel_us) {
+  croq::clear_error();
+  if (sm_mhz == nullptr || kernel_us == nullptr) return CROQ_ERR_NULL;
+  int rc = CROQ_OK;
+  croq::DeviceState* st = croq::device_state(&rc);
+  if (st == nullptr) return rc;
+  const volatile unsigned long long* w =
+      reinterpret_cast<const volatile unsigned long long*>(st->status_host + 2);
+  const unsigned long long cycles = w[0], ns = w[1];
+  *kernel_us = static_cast<double>(ns) * 1e-3;
+  *sm_mhz = ns != 0 ? static_cast<double>(cycles) * 1e3 / static_cast<double>(ns) : 0.0;
+  return CROQ_OK;
+}
+
 int croq_synchronize(croq_stream stream) {
   croq::clear_error();
   int rc = CROQ_OK;

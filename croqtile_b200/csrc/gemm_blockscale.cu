@@ -110,6 +110,8 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_word;
+  ClockProbe probe;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.begin();
 
   if (warp < 4) {
     reg_dealloc<56>();
@@ -260,6 +262,7 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
 }
 
 template <bool kBf16>

@@ -49,6 +49,7 @@ struct WorkTile {
   bool valid;
 };
 
+template <int kTileM, int kTileN>
 __device__ __forceinline__ WorkTile decode_work(const DenseParams& p, int w) {
   WorkTile t;
   const int subs = p.sub_m * p.sub_n;
@@ -70,8 +71,8 @@ __device__ __forceinline__ WorkTile decode_work(const DenseParams& p, int w) {
   }
   const int si = s / p.sub_n;
   const int sj = s - si * p.sub_n;
-  t.m0 = bm * p.tile_m + si * kBlockM;
-  t.n0 = bn * p.tile_n + sj * kBlockN;
+  t.m0 = bm * p.tile_m + si * kTileM;
+  t.n0 = bn * p.tile_n + sj * kTileN;
   t.m_end = min(p.M, (bm + 1) * p.tile_m);
   t.n_end = min(p.N, (bn + 1) * p.tile_n);
   t.valid = (t.m0 < t.m_end) && (t.n0 < t.n_end);
@@ -122,6 +123,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_word;
+  ClockProbe probe;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.begin();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -129,7 +132,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-      const WorkTile t = decode_work(p, w);
+      const WorkTile t = decode_work<kBlockM, kBlockN>(p, w);
       if (!t.valid) continue;
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
@@ -162,7 +165,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-      const WorkTile t = decode_work(p, w);
+      const WorkTile t = decode_work<kBlockM, kBlockN>(p, w);
       if (!t.valid) continue;
       ok = mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr);
       if (!ok) break;
@@ -204,7 +207,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-      const WorkTile t = decode_work(p, w);
+      const WorkTile t = decode_work<kBlockM, kBlockN>(p, w);
       if (!t.valid) continue;
       ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
       if (!ok) break;
@@ -253,6 +256,202 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
+}
+
+// ------------------------------------------------------------ CTA-pair form --
+// Two CTAs of a cluster share one 256x256 accumulator tile: each loads its own
+// 128 rows of A and its own 128 rows of B (no multicast), rank 0 issues
+// tcgen05.mma.cta_group::2 (M=256, N=256) over both shared memories, and each
+// CTA's TMEM receives its 128 output rows. Per CTA this moves 32 KB of
+// operands per 64-wide K step instead of 48 KB, which is what bounds the
+// single-CTA form (operand traffic from L2).
+constexpr int kPairM = 256;
+constexpr int kPairN = 256;
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairABytes = 128 * kBlockK * 2;
+constexpr uint32_t kPairBBytes = 128 * kBlockK * 2;
+constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                       const __grid_constant__ CUtensorMap map_b, const DenseParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];    // used in rank 0
+  __shared__ __align__(8) uint64_t bar_empty[kPairStages];   // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_full[2];          // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];         // used in rank 0
+  __shared__ __align__(8) uint64_t bar_drain;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 8);  // four epilogue warps in each CTA
+    }
+    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();   // barriers of both CTAs are initialised before any remote arrive
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_word;
+  ClockProbe probe;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.begin();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      const WorkTile t = decode_work<kPairM, kPairN>(p, w);
+      if (!t.valid) continue;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
+          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2u * kPairStageBytes);
+          tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, t.m0 + static_cast<int>(rank) * 128);
+          tma_load_2d_pair(a_dst + kPairABytes, &map_b, full_leader, kb * kBlockK,
+                           t.n0 + static_cast<int>(rank) * 128);
+        }
+        __syncwarp();
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 1000000ull) {
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------- MMA issuer (leader CTA) --
+    constexpr uint32_t idesc =
+        umma_idesc(kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16, kPairM, kPairN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      const WorkTile t = decode_work<kPairM, kPairN>(p, w);
+      if (!t.valid) continue;
+      ok = mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_ptr);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kPairN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_src = smem_base + stage * kPairStageBytes;
+          const uint64_t adesc = umma_desc_k_sw128(a_src);
+          const uint64_t bdesc = umma_desc_k_sw128(a_src + kPairABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            umma_f16_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(smem_u32(&bar_empty[stage]), 3);   // frees the stage in both CTAs
+        }
+        __syncwarp();
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit_pair(smem_u32(&bar_acc_full[acc]), 3);
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) umma_commit_pair(smem_u32(&bar_drain), 1);
+    __syncwarp();
+    mbar_wait(smem_u32(&bar_drain), 0, abort_ptr);
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;
+    const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      const WorkTile t = decode_work<kPairM, kPairN>(p, w);
+      if (!t.valid) continue;
+      ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = t.m0 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const uint32_t taddr =
+          tmem_base + static_cast<uint32_t>(acc * kPairN) + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+      for (int c = 0; c < kPairN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait_on(v);
+        const int col0 = t.n0 + c * 32;
+        if (row < t.m_end && col0 < t.n_end) {
+          if (vec_ok && ((col0 & 7) == 0) && col0 + 32 <= t.n_end) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < t.n_end) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // Neither CTA may retire while its peer can still signal its barriers or
+  // the shared MMA can still touch its shared memory or TMEM.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
 }
 
 int check_dense_views(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
@@ -304,8 +503,13 @@ int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2*
   p.tile_n = sched_tile_n;
   p.tiles_m = (M + sched_tile_m - 1) / sched_tile_m;
   p.tiles_n = (N + sched_tile_n - 1) / sched_tile_n;
-  p.sub_m = (sched_tile_m + kBlockM - 1) / kBlockM;
-  p.sub_n = (sched_tile_n + kBlockN - 1) / kBlockN;
+  // The CTA-pair kernel owns 256x256 tiles; schedule tiles smaller than that in
+  // either direction (the reference's 64x128, say) run on the single-CTA kernel.
+  const bool use_pair = (sched_tile_m % kPairM == 0) && (sched_tile_n % kPairN == 0) &&
+                        st->sm_count >= 2;
+  const int bm = use_pair ? kPairM : kBlockM, bn = use_pair ? kPairN : kBlockN;
+  p.sub_m = (sched_tile_m + bm - 1) / bm;
+  p.sub_n = (sched_tile_n + bn - 1) / bn;
   const long long total = 1ll * p.tiles_m * p.tiles_n * p.sub_m * p.sub_n;
   if (total > 0x7FFFFFFFll) return CROQ_ERR_SHAPE;
   p.total_work = static_cast<int>(total);
@@ -314,20 +518,28 @@ int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2*
   const CUtensorMapDataType dt =
       kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap map_a, map_b;
-  rc = encode_tensor_map_2d(&map_a, dt, 2, lhs->ptr, M, K, kBlockM, kBlockK);
+  rc = encode_tensor_map_2d(&map_a, dt, 2, lhs->ptr, M, K, 128, kBlockK);
   if (rc != CROQ_OK) return rc;
-  rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, kBlockN, kBlockK);
+  rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, use_pair ? 128 : kBlockN, kBlockK);
   if (rc != CROQ_OK) return rc;
 
-  auto kernel = gemm_dense_kernel<kBf16>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[kBf16 ? 1 : 0]) {
-    CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CROQ_CUDA_TRY(cudaFuncSetAttribute(gemm_dense_kernel<kBf16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kSmemBytes)));
+    CROQ_CUDA_TRY(cudaFuncSetAttribute(gemm_dense_pair_kernel<kBf16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kPairSmemBytes)));
     attr_set[kBf16 ? 1 : 0] = true;
   }
-  const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  if (use_pair) {
+    const int pairs = p.total_work < st->sm_count / 2 ? p.total_work : st->sm_count / 2;
+    gemm_dense_pair_kernel<kBf16><<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(map_a, map_b, p);
+  } else {
+    const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+    gemm_dense_kernel<kBf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  }
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

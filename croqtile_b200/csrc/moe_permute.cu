@@ -1,0 +1,245 @@
+// MoE row movement for sm_100a: gather into expert order (optionally fused
+// with the 1x128 e4m3 activation quantiser), the stand-alone row quantiser,
+// and the weighted combine back into token order.
+//
+// All four are HBM-bound: one CTA per destination row, 128-bit loads and
+// stores along the row, warp shuffles for the per-block amax. Algorithmic
+// bytes per row of H bf16 elements: permute 2H read + 2H written (+4 B index);
+// permute+quant 2H read + H + 4*H/128 written; combine k*2H read + 2H written.
+// The reference has no counterpart for these kernels; the contract is stated
+// with the entry points in croq_b200.h.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "croq_device.cuh"
+#include "croq_host.h"
+
+namespace croq {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+// dst[pos,:] = src[perm_to_src[pos] / k, :]   (perm == nullptr: identity rows)
+__global__ void __launch_bounds__(kRowThreads)
+moe_permute_kernel(const uint16_t* __restrict__ src, const int* __restrict__ perm_to_src, int k,
+                   int T, int H, uint16_t* __restrict__ dst, int* __restrict__ status) {
+  const int pos = blockIdx.x;
+  const int r = perm_to_src[pos];
+  const int t = r / k;
+  if (r < 0 || t >= T) {
+    if (threadIdx.x == 0) *status = kDevBadIndex;
+    return;
+  }
+  const uint16_t* s = src + static_cast<size_t>(t) * H;
+  uint16_t* d = dst + static_cast<size_t>(pos) * H;
+  if ((H & 7) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(s);
+    uint4* d4 = reinterpret_cast<uint4*>(d);
+    for (int i = threadIdx.x; i < H / 8; i += kRowThreads) d4[i] = __ldg(s4 + i);
+  } else {
+    for (int i = threadIdx.x; i < H; i += kRowThreads) d[i] = s[i];
+  }
+}
+
+// Row gather + per-128 quantiser. Each thread owns chunks of 8 consecutive
+// elements; the 16 lanes that share a 128-wide block reduce amax by shuffles.
+// H must be a multiple of 128.
+__global__ void __launch_bounds__(kRowThreads)
+moe_quant_rows_kernel(const uint16_t* __restrict__ src, const int* __restrict__ perm_to_src,
+                      int k, int T, int H, uint8_t* __restrict__ dst_q,
+                      float* __restrict__ dst_scale, int* __restrict__ status) {
+  const int pos = blockIdx.x;
+  int t = pos;
+  if (perm_to_src != nullptr) {
+    const int r = perm_to_src[pos];
+    t = r / k;
+    if (r < 0 || t >= T) {
+      if (threadIdx.x == 0) *status = kDevBadIndex;
+      return;
+    }
+  }
+  const uint4* s4 = reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * H);
+  uint2* q2 = reinterpret_cast<uint2*>(dst_q + static_cast<size_t>(pos) * H);
+  float* sc = dst_scale + static_cast<size_t>(pos) * (H / 128);
+  const int chunks = H / 8;
+  // chunks is a multiple of 16, so whole 16-lane groups are active together
+  for (int c = threadIdx.x; c < chunks; c += kRowThreads) {
+    const uint4 raw = __ldg(s4 + c);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[2 * i] = bf16_bits_to_f32(w[i] & 0xFFFFu);
+      x[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    const unsigned group = 0xFFFFu << (threadIdx.x & 16);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group, amax, o));
+    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+      hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[4 + i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    q2[c] = make_uint2(lo, hi);
+    if ((threadIdx.x & 15) == 0) sc[c >> 4] = scale;
+  }
+}
+
+// out[t,:] = RN_bf16( sum_j w[t,j] * y[src_to_perm[t*k+j], :] ), ascending j.
+template <int kMaxK>
+__global__ void __launch_bounds__(kRowThreads)
+moe_unpermute_kernel(const uint16_t* __restrict__ y, const int* __restrict__ src_to_perm,
+                     const float* __restrict__ topk_w, int k, int rows, int H,
+                     uint16_t* __restrict__ out, int* __restrict__ status) {
+  __shared__ int pos_s[kMaxK];
+  __shared__ float w_s[kMaxK];
+  __shared__ int bad;
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  if (threadIdx.x < k) {
+    const int p = src_to_perm[static_cast<size_t>(t) * k + threadIdx.x];
+    if (p < 0 || p >= rows) { bad = 1; *status = kDevBadIndex; }
+    pos_s[threadIdx.x] = p;
+    w_s[threadIdx.x] = topk_w[static_cast<size_t>(t) * k + threadIdx.x];
+  }
+  __syncthreads();
+  if (bad) return;
+  uint16_t* o = out + static_cast<size_t>(t) * H;
+  if ((H & 7) == 0) {
+    for (int c = threadIdx.x; c < H / 8; c += kRowThreads) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+      for (int j = 0; j < k; ++j) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + static_cast<size_t>(pos_s[j]) * H) + c);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        const float wj = w_s[j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] = fmaf(wj, bf16_bits_to_f32(w[i] & 0xFFFFu), acc[2 * i]);
+          acc[2 * i + 1] = fmaf(wj, bf16_bits_to_f32(w[i] >> 16), acc[2 * i + 1]);
+        }
+      }
+      uint4 pk;
+      pk.x = pack2<true>(acc[0], acc[1]);
+      pk.y = pack2<true>(acc[2], acc[3]);
+      pk.z = pack2<true>(acc[4], acc[5]);
+      pk.w = pack2<true>(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(o)[c] = pk;
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += kRowThreads) {
+      float acc = 0.0f;
+      for (int j = 0; j < k; ++j)
+        acc = fmaf(w_s[j], bf16_bits_to_f32(y[static_cast<size_t>(pos_s[j]) * H + c]), acc);
+      o[c] = pack1<true>(acc);
+    }
+  }
+}
+
+int launch_quant(const croq_view2* src, const croq_view1* perm, int k, const croq_view2* dst_q,
+                 const croq_view2* dst_scale, croq_stream stream_) {
+  if (!view_ok(src) || !view_ok(dst_q) || !view_ok(dst_scale)) return CROQ_ERR_NULL;
+  if (perm != nullptr && !view_ok(perm)) return CROQ_ERR_NULL;
+  const size_t T = src->dims[0], H = src->dims[1];
+  const size_t rows = perm != nullptr ? perm->dims[0] : T;
+  if (perm != nullptr && k <= 0) return CROQ_ERR_SHAPE;
+  if (dst_q->dims[0] != rows || dst_q->dims[1] != H) return CROQ_ERR_SHAPE;
+  if (H % 128 != 0) return CROQ_ERR_UNSUPPORTED;
+  if (dst_scale->dims[0] != rows || dst_scale->dims[1] != H / 128) return CROQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFull || T > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (!aligned16(src->ptr) || (reinterpret_cast<uintptr_t>(dst_q->ptr) & 7u) != 0 ||
+      (reinterpret_cast<uintptr_t>(dst_scale->ptr) & 3u) != 0)
+    return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (rows == 0) return CROQ_OK;
+  moe_quant_rows_kernel<<<static_cast<unsigned>(rows), kRowThreads, 0,
+                          static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint16_t*>(src->ptr),
+      perm != nullptr ? static_cast<const int*>(perm->ptr) : nullptr, k, static_cast<int>(T),
+      static_cast<int>(H), static_cast<uint8_t*>(dst_q->ptr), static_cast<float*>(dst_scale->ptr),
+      st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+}  // namespace
+
+}  // namespace croq
+
+extern "C" {
+
+int croq_moe_permute(const croq_view2* src, const croq_view1* perm_to_src, int k,
+                     const croq_view2* dst, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(src) || !view_ok(perm_to_src) || !view_ok(dst)) return CROQ_ERR_NULL;
+  const size_t T = src->dims[0], H = src->dims[1], rows = perm_to_src->dims[0];
+  if (k <= 0) return CROQ_ERR_SHAPE;
+  if (dst->dims[0] != rows || dst->dims[1] != H) return CROQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFull || T > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if ((H & 7) == 0 && (!aligned16(src->ptr) || !aligned16(dst->ptr))) return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (rows == 0 || H == 0) return CROQ_OK;
+  moe_permute_kernel<<<static_cast<unsigned>(rows), kRowThreads, 0,
+                       static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint16_t*>(src->ptr), static_cast<const int*>(perm_to_src->ptr), k,
+      static_cast<int>(T), static_cast<int>(H), static_cast<uint16_t*>(dst->ptr), st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+int croq_moe_permute_quant_e4m3(const croq_view2* src, const croq_view1* perm_to_src, int k,
+                                const croq_view2* dst_q, const croq_view2* dst_scale,
+                                croq_stream stream) {
+  croq::clear_error();
+  if (perm_to_src == nullptr) return CROQ_ERR_NULL;
+  return croq::launch_quant(src, perm_to_src, k, dst_q, dst_scale, stream);
+}
+
+int croq_quant_rows_e4m3(const croq_view2* x, const croq_view2* q, const croq_view2* scale,
+                         croq_stream stream) {
+  croq::clear_error();
+  return croq::launch_quant(x, nullptr, 1, q, scale, stream);
+}
+
+int croq_moe_unpermute(const croq_view2* y, const croq_view1* src_to_perm,
+                       const croq_view2* topk_w, const croq_view2* out, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(y) || !view_ok(src_to_perm) || !view_ok(topk_w) || !view_ok(out)) return CROQ_ERR_NULL;
+  const size_t rows = y->dims[0], H = y->dims[1], T = topk_w->dims[0], k = topk_w->dims[1];
+  if (k == 0 || k > 32) return CROQ_ERR_SHAPE;
+  if (src_to_perm->dims[0] != T * k || rows != T * k) return CROQ_ERR_SHAPE;
+  if (out->dims[0] != T || out->dims[1] != H) return CROQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if ((H & 7) == 0 && (!aligned16(y->ptr) || !aligned16(out->ptr))) return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (T == 0 || H == 0) return CROQ_OK;
+  moe_unpermute_kernel<32><<<static_cast<unsigned>(T), kRowThreads, 0,
+                             static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint16_t*>(y->ptr), static_cast<const int*>(src_to_perm->ptr),
+      static_cast<const float*>(topk_w->ptr), static_cast<int>(k), static_cast<int>(rows),
+      static_cast<int>(H), static_cast<uint16_t*>(out->ptr), st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+}  // extern "C"

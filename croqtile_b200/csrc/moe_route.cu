@@ -1,0 +1,259 @@
+// MoE routing for sm_100a: top-k over raw logits, softmax weights, per-expert
+// counts, exclusive offsets and the stable token permutation.
+//
+// The reference has no routing code; the contract is the one stated with
+// croq_moe_route_topk in croq_b200.h. Indices, counts, offsets and both
+// permutation maps are pure integer results and do not depend on launch
+// geometry: ordering is (logit descending, expert ascending) on raw logits and
+// the permutation is a stable counting sort on the expanded row index t*k+j.
+//
+// Three launches, all bandwidth/latency bound (16 MB of logits at T=16384):
+//   topk_kernel  one warp per token, logits held in registers, k rounds of a
+//                warp arg-max on a 64-bit (sortable value, inverted index) key;
+//                per-CTA expert histogram in shared memory -> block_counts
+//   scan_kernel  one CTA: per expert an exclusive scan over CTAs (stable
+//                block bases), then a warp-shuffle scan over experts (offsets)
+//   perm_kernel  one warp per chunk of rows walks it in order; __match_any
+//                ranks rows of equal expert inside a 32-row group
+#include "croq_device.cuh"
+#include "croq_host.h"
+
+namespace croq {
+
+namespace {
+
+constexpr int kTokensPerBlock = 64;
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxExperts = 1024;
+
+// Monotone map float -> uint32 with -0 folded into +0 and NaN below -inf, so
+// that NaN logits are chosen last and ties fall to the lower expert index.
+__device__ __forceinline__ uint32_t sortable_key(float v) {
+  if (v != v) return 0u;
+  v += 0.0f;
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+template <int kItems>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+moe_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int norm_topk,
+                int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                int* __restrict__ block_counts) {
+  __shared__ int hist[kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+
+  const int tok0 = blockIdx.x * kTokensPerBlock;
+  for (int tt = warp; tt < kTokensPerBlock; tt += kWarpsPerBlock) {
+    const int t = tok0 + tt;
+    if (t >= T) break;
+    const float* row = logits + static_cast<size_t>(t) * E;
+    float v[kItems];
+    unsigned long long key[kItems];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = (e < E) ? __ldg(row + e) : -INFINITY;
+      // inverted index in the low word: larger key == lower expert index
+      key[i] = (e < E) ? ((static_cast<unsigned long long>(sortable_key(v[i])) << 32) |
+                          static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(e)))
+                       : 0ull;
+      if (e < E && v[i] > mx) mx = v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float denom = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i)
+      if (lane + 32 * i < E) denom += expf(v[i] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+
+    float my_w = 0.0f;   // lane j keeps the weight of the j-th pick (k <= 32)
+    int my_e = 0;
+    for (int j = 0; j < k; ++j) {
+      unsigned long long best = 0ull;
+#pragma unroll
+      for (int i = 0; i < kItems; ++i) best = key[i] > best ? key[i] : best;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+      }
+      const int e_sel = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull));
+      // the owner lane retires the pick and publishes its logit
+      float l_sel = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kItems; ++i)
+        if (lane + 32 * i == e_sel) { l_sel = v[i]; key[i] = 0ull; }
+      l_sel = __shfl_sync(0xffffffffu, l_sel, e_sel & 31);
+      const float w = expf(l_sel - mx) / denom;
+      if (lane == j) { my_w = w; my_e = e_sel; }
+    }
+    if (norm_topk) {
+      float wsum = 0.0f;
+      for (int j = 0; j < k; ++j) wsum += __shfl_sync(0xffffffffu, my_w, j);  // ascending j
+      my_w = my_w / wsum;
+    }
+    if (lane < k) {
+      topk_idx[static_cast<size_t>(t) * k + lane] = my_e;
+      topk_w[static_cast<size_t>(t) * k + lane] = my_w;
+      atomicAdd(&hist[my_e], 1);
+    }
+  }
+  __syncthreads();
+  int* out = block_counts + static_cast<size_t>(blockIdx.x) * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) out[e] = hist[e];
+}
+
+// block_counts[b][e] becomes the number of rows of expert e in CTAs before b;
+// counts[e] the total; offsets the exclusive scan of counts (length E+1).
+__global__ void __launch_bounds__(1024)
+moe_scan_kernel(int* __restrict__ block_counts, int num_blocks, int E, int* __restrict__ counts,
+                int* __restrict__ offsets) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < E; base += blockDim.x) {
+    const int e = base + threadIdx.x;
+    int total = 0;
+    if (e < E) {
+      for (int b = 0; b < num_blocks; ++b) {
+        int* p = block_counts + static_cast<size_t>(b) * E + e;
+        const int c = *p;
+        *p = total;
+        total += c;
+      }
+      counts[e] = total;
+    }
+    // exclusive scan of `total` across the CTA
+    int incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int s = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, s, o);
+        if (lane >= o) s += n;
+      }
+      warp_sums[lane] = s;   // inclusive over warps
+    }
+    __syncthreads();
+    const int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - total;
+    if (e < E) offsets[e] = before;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = before + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[E] = carry;
+}
+
+__global__ void __launch_bounds__(32)
+moe_perm_kernel(const int* __restrict__ topk_idx, const int* __restrict__ block_base,
+                const int* __restrict__ offsets, int rows_total, int rows_per_block, int E,
+                int* __restrict__ perm_to_src, int* __restrict__ src_to_perm,
+                int* __restrict__ status) {
+  __shared__ int cursor[kMaxExperts];
+  const int lane = threadIdx.x;
+  const int* base = block_base + static_cast<size_t>(blockIdx.x) * E;
+  for (int e = lane; e < E; e += 32) cursor[e] = offsets[e] + base[e];
+  __syncwarp();
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(rows_total, r0 + rows_per_block);
+  for (int g = r0; g < r1; g += 32) {
+    const int r = g + lane;
+    const bool active = r < r1;
+    const unsigned amask = __ballot_sync(0xffffffffu, active);
+    if (active) {
+      int e = topk_idx[r];
+      if (e < 0 || e >= E) { *status = kDevBadIndex; e = 0; }
+      const unsigned same = __match_any_sync(amask, e);
+      const int rank = __popc(same & ((1u << lane) - 1u));
+      const int start = cursor[e];
+      __syncwarp(amask);
+      if (rank == 0) cursor[e] = start + __popc(same);
+      __syncwarp(amask);
+      const int pos = start + rank;
+      src_to_perm[r] = pos;
+      if (pos >= 0 && pos < rows_total) perm_to_src[pos] = r; else *status = kDevBadIndex;
+    }
+  }
+}
+
+}  // namespace
+
+}  // namespace croq
+
+extern "C" int croq_moe_route_topk(const croq_view2* logits, int k, int norm_topk,
+                                   const croq_view2* topk_idx, const croq_view2* topk_w,
+                                   const croq_view1* expert_counts,
+                                   const croq_view1* expert_offsets,
+                                   const croq_view1* perm_to_src, const croq_view1* src_to_perm,
+                                   croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(logits) || !view_ok(topk_idx) || !view_ok(topk_w) || !view_ok(expert_counts) ||
+      !view_ok(expert_offsets) || !view_ok(perm_to_src) || !view_ok(src_to_perm))
+    return CROQ_ERR_NULL;
+  const size_t T = logits->dims[0], E = logits->dims[1];
+  if (k <= 0 || k > 32 || static_cast<size_t>(k) > E) return CROQ_ERR_SHAPE;
+  if (E == 0 || E > kMaxExperts) return CROQ_ERR_UNSUPPORTED;
+  if (T * static_cast<size_t>(k) > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (topk_idx->dims[0] != T || topk_idx->dims[1] != static_cast<size_t>(k)) return CROQ_ERR_SHAPE;
+  if (topk_w->dims[0] != T || topk_w->dims[1] != static_cast<size_t>(k)) return CROQ_ERR_SHAPE;
+  if (expert_counts->dims[0] != E || expert_offsets->dims[0] != E + 1) return CROQ_ERR_SHAPE;
+  if (perm_to_src->dims[0] != T * k || src_to_perm->dims[0] != T * k) return CROQ_ERR_SHAPE;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int* counts = static_cast<int*>(expert_counts->ptr);
+  int* offsets = static_cast<int*>(expert_offsets->ptr);
+  if (T == 0) {
+    CROQ_CUDA_TRY(cudaMemsetAsync(counts, 0, E * sizeof(int), stream));
+    CROQ_CUDA_TRY(cudaMemsetAsync(offsets, 0, (E + 1) * sizeof(int), stream));
+    return CROQ_OK;
+  }
+  const int num_blocks = static_cast<int>((T + kTokensPerBlock - 1) / kTokensPerBlock);
+  // Scratch: one histogram row per top-k CTA, allocated in stream order.
+  int* block_counts = nullptr;
+  CROQ_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&block_counts),
+                                static_cast<size_t>(num_blocks) * E * sizeof(int), stream));
+  const float* lg = static_cast<const float*>(logits->ptr);
+  int* idx = static_cast<int*>(topk_idx->ptr);
+  float* w = static_cast<float*>(topk_w->ptr);
+  const int Ti = static_cast<int>(T), Ei = static_cast<int>(E);
+  const dim3 block(kWarpsPerBlock * 32);
+  if (E <= 256)
+    moe_topk_kernel<8><<<num_blocks, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, block_counts);
+  else if (E <= 512)
+    moe_topk_kernel<16><<<num_blocks, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, block_counts);
+  else
+    moe_topk_kernel<32><<<num_blocks, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, block_counts);
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) {
+    moe_scan_kernel<<<1, 1024, 0, stream>>>(block_counts, num_blocks, Ei, counts, offsets);
+    err = cudaGetLastError();
+  }
+  if (err == cudaSuccess) {
+    moe_perm_kernel<<<num_blocks, 32, 0, stream>>>(
+        idx, block_counts, offsets, static_cast<int>(T * k), kTokensPerBlock * k, Ei,
+        static_cast<int*>(perm_to_src->ptr), static_cast<int*>(src_to_perm->ptr), st->status_dev);
+    err = cudaGetLastError();
+  }
+  cudaError_t free_err = cudaFreeAsync(block_counts, stream);
+  if (err != cudaSuccess) return record_cuda_error(err, "moe routing launch");
+  if (free_err != cudaSuccess) return record_cuda_error(free_err, "cudaFreeAsync");
+  return CROQ_OK;
+}

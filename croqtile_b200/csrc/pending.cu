@@ -6,28 +6,9 @@ int croq_gemm_sp_f16(const croq_view2*, const croq_view2*, const croq_view2*, co
                      int, croq_stream) {
   return CROQ_ERR_UNSUPPORTED;
 }
-int croq_moe_route_topk(const croq_view2*, int, int, const croq_view2*, const croq_view2*,
-                        const croq_view1*, const croq_view1*, const croq_view1*,
-                        const croq_view1*, croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
-int croq_moe_permute(const croq_view2*, const croq_view1*, int, const croq_view2*, croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
-int croq_moe_permute_quant_e4m3(const croq_view2*, const croq_view1*, int, const croq_view2*,
-                                const croq_view2*, croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
-int croq_moe_unpermute(const croq_view2*, const croq_view1*, const croq_view2*,
-                       const croq_view2*, croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
 int croq_moe_grouped_gemm_e4m3(const croq_view2*, const croq_view2*, const croq_view3*,
                                const croq_view3*, const croq_view1*, const croq_view2*, int,
                                croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
-int croq_quant_rows_e4m3(const croq_view2*, const croq_view2*, const croq_view2*, croq_stream) {
   return CROQ_ERR_UNSUPPORTED;
 }
 }

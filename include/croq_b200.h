@@ -63,6 +63,12 @@ const char* croq_version(void);
  * wrapper (cute_codegen.cpp:3748-3754). */
 int croq_synchronize(croq_stream stream);
 
+/* SM clock (MHz) and duration (us) that CTA 0 of the most recent GEMM kernel on
+ * the current device measured on itself (cycle counter over wall clock); call
+ * after croq_synchronize. Diagnostic for benchmarks: tells a power-capped run
+ * from a slow kernel. No counterpart in the reference. */
+int croq_last_kernel_clock(double* sm_mhz, double* kernel_us);
+
 /* Persistent GEMM with a caller-supplied tile schedule.
  * Replaces `__co__ matmul_persis_hilbert_sm90(lhs, rhs, output, schedule_m,
  * schedule_n)` (tests/gpu/end2end/wgmma_persis.co:5-33; README.md:82-107):
