@@ -23,6 +23,9 @@ enum DeviceStatus : int {
 };
 
 // Wall-clock budget of one wait, in nanoseconds of %globaltimer.
+#ifndef CROQ_FAST_POLLS
+#define CROQ_FAST_POLLS 64
+#endif
 #ifndef CROQ_WAIT_BUDGET_NS
 #define CROQ_WAIT_BUDGET_NS 1000000000ull
 #endif
@@ -106,12 +109,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Waits for the phase with the given parity to complete. Returns false when
 // the budget ran out or another role already aborted; the caller then leaves
-// its loops and walks to the common teardown.
+// its loops and walks to the common teardown. The first polls use the
+// non-suspending test_wait (a ready barrier costs a few tens of cycles instead
+// of the ~130 a try_wait takes to come back); a long wait falls back to
+// try_wait, which parks the thread between polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_word) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int i = 0; i < CROQ_FAST_POLLS; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   for (;;) {
@@ -387,6 +409,24 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, ui
       "}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// Two independent fp32 fused multiply-adds in one instruction:
+// d.x = a_lo * b.x + d.x and d.y = a_hi * b.y + d.y, each rounded once (IEEE).
+// The accumulator pair lives in one 64-bit register.
+__device__ __forceinline__ void ffma2(float2& d, uint32_t a_lo_bits, uint32_t a_hi_bits,
+                                      unsigned long long b_packed) {
+  unsigned long long aa;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(aa) : "r"(a_lo_bits), "r"(a_hi_bits));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(aa), "l"(b_packed));
+}
+
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
 
 // ------------------------------------------------------------- conversions --

@@ -12,14 +12,15 @@
 //
 // In the reference the consumer warpgroup alternates WGMMA and the CUDA-core
 // promotion, so the tensor pipe idles during every promotion. Here the two
-// run concurrently: the MMA warp writes the partial product of K block kb
-// into one of two 256-column TMEM buffers while eight epilogue warps drain
-// the other buffer into register accumulators.
+// run concurrently: the partial product of K block kb is written into one of
+// two 256-column TMEM buffers while sixteen epilogue warps drain the other into
+// register accumulators with packed two-wide fp32 FMAs.
 //   warp 0      TMA producer (128x128 A tile + 256x128 B tile per stage)
-//   warp 1      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 128x256x32 per K block
+//   warps 1,3   MMA issuers (even / odd K blocks): 4 x tcgen05.mma kind::f8f6f4
+//               128x256x32 per K block, one commit
 //   warp 2      TMEM allocation
-//   warps 4-11  promotion + store; warp w reads TMEM lanes 32*(w%4).., columns
-//               128*((w-4)/4).. and keeps 128 fp32 accumulators per thread
+//   warps 4-19  promotion + store; warp w reads TMEM lanes 32*(w%4).., columns
+//               64*((w-4)/4).. and keeps 64 fp32 accumulators per thread
 #include "croq_device.cuh"
 #include "croq_host.h"
 
@@ -32,7 +33,17 @@ constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // one scale block; 128 x 1 B = one swizzle row
 constexpr int kUmmaK = 32;
 constexpr int kStages = 4;
-constexpr int kThreads = 384;
+constexpr int kThreads = 640;        // 4 control warps + 16 promotion warps
+constexpr int kEpiWarps = 16;
+// Register hand-off between warpgroups (setmaxnreg). A CTA can only re-assign
+// registers it owns: what the control warpgroup gives up must cover what the
+// promotion warpgroups take, or setmaxnreg.inc would wait forever.
+constexpr int kLaunchRegs = 96;   // per thread at launch: 65536 / 640, rounded down to 8
+constexpr int kCtrlRegs = 32;
+constexpr int kEpiRegs = 112;
+static_assert((kLaunchRegs - kCtrlRegs) * 128 >= (kEpiRegs - kLaunchRegs) * kEpiWarps * 32,
+              "control warps do not release enough registers for the promotion warps");
+static_assert(kLaunchRegs * kThreads <= 65536, "launch allocation exceeds the register file");
 constexpr int kTmemCols = 512;
 constexpr uint32_t kABytes = kBlockM * kBlockK;
 constexpr uint32_t kBBytes = kBlockN * kBlockK;
@@ -71,11 +82,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, const BlockScaleParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages];
-  __shared__ __align__(8) uint64_t bar_empty[kStages];
-  __shared__ __align__(8) uint64_t bar_part_full[2];
-  __shared__ __align__(8) uint64_t bar_part_empty[2];
-  __shared__ __align__(8) uint64_t bar_drain;
+  __shared__ __align__(8) uint64_t bar_full[kStages];      // TMA data of a stage has landed
+  __shared__ __align__(8) uint64_t bar_mma_done[kStages];  // the stage's MMAs retired: the
+                                                           // smem stage is free AND its TMEM
+                                                           // partial is complete
+  __shared__ __align__(8) uint64_t bar_part_empty[2];      // a TMEM partial buffer was drained
+  __shared__ __align__(8) uint64_t bar_drain[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
 
@@ -83,18 +95,20 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int num_kb = p.KB;
+  const int my_tiles = (p.total_work - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+  const int total_kb = my_tiles * num_kb;   // K blocks this CTA walks, over all its tiles
 
   if (threadIdx.x == 0) {
     abort_word = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_mma_done[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_part_full[b]), 1);
-      mbar_init(smem_u32(&bar_part_empty[b]), 8);  // one arrival per promotion warp
+      mbar_init(smem_u32(&bar_part_empty[b]), kEpiWarps);  // one arrival per promotion warp
+      mbar_init(smem_u32(&bar_drain[b]), 1);
     }
-    mbar_init(smem_u32(&bar_drain), 1);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -114,7 +128,10 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   if (blockIdx.x == 0 && threadIdx.x == 0) probe.begin();
 
   if (warp < 4) {
-    reg_dealloc<56>();
+    reg_dealloc<kCtrlRegs>();
+    // The control loops run warp-uniformly (all 32 lanes wait and compute the
+    // descriptors, so those values stay in uniform registers) and only the
+    // asynchronous instructions themselves are issued by one elected lane.
     if (warp == 0) {
       // ---------------------------------------------------------- producer --
       int stage = 0;
@@ -124,16 +141,15 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
         int m0, n0;
         decode_tile(p, w, m0, n0);
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
+          ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase ^ 1u, abort_ptr);
           if (!ok) break;
-          if (lane == 0) {
-            const uint32_t full = smem_u32(&bar_full[stage]);
-            const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          if (elect_one()) {
             mbar_arrive_expect_tx(full, kStageBytes);
             tma_load_2d(a_dst, &map_a, full, kb * kBlockK, m0);
             tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, n0);
           }
-          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -142,113 +158,113 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
         while (global_timer_ns() - t0 < 1000000ull) {
         }
       }
-    } else if (warp == 1) {
-      // -------------------------------------------------------- MMA issuer --
+    } else if (warp == 1 || warp == 3) {
+      // ------------------------------------------------------- MMA issuers --
+      // Two warps alternate: warp 1 takes the even K blocks (TMEM buffer 0),
+      // warp 3 the odd ones (buffer 1). The blocks are independent (each starts
+      // a fresh partial), so no order between the two is needed. One commit per
+      // K block signals both "stage free" and "partial complete".
       constexpr uint32_t idesc = umma_idesc(kFmtE4M3, kFmtE4M3, kBlockM, kBlockN);
-      int stage = 0;
-      uint32_t phase = 0;
-      int buf = 0;
-      uint32_t buf_phase = 0;
+      const int buf = (warp == 1) ? 0 : 1;
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBlockN);
+      const uint32_t empty_bar = smem_u32(&bar_part_empty[buf]);
       bool ok = true;
-      for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(smem_u32(&bar_part_empty[buf]), buf_phase ^ 1u, abort_ptr);
-          if (!ok) break;
-          ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
-          if (!ok) break;
-          tc_fence_after_sync();
-          if (lane == 0) {
-            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBlockN);
-            const uint32_t a_src = smem_base + stage * kStageBytes;
-            const uint64_t adesc = umma_desc_k_sw128(a_src);
-            const uint64_t bdesc = umma_desc_k_sw128(a_src + kABytes);
-#pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-              umma_f8(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, k != 0 ? 1u : 0u);
-            }
-            umma_commit(smem_u32(&bar_empty[stage]));
-            umma_commit(smem_u32(&bar_part_full[buf]));
-          }
-          __syncwarp();
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-          buf ^= 1;
-          if (buf == 0) buf_phase ^= 1u;
+      for (int g = buf; g < total_kb; g += 2) {
+        const int stage = g % kStages;
+        const uint32_t phase = static_cast<uint32_t>(g / kStages) & 1u;
+        const uint32_t buf_phase = static_cast<uint32_t>(g >> 1) & 1u;
+        const uint32_t a_src = smem_base + stage * kStageBytes;
+        const uint64_t adesc = umma_desc_k_sw128(a_src);
+        const uint64_t bdesc = umma_desc_k_sw128(a_src + kABytes);
+        // operands usually land long before the partial buffer is free
+        ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+        if (!ok) break;
+        ok = mbar_wait(empty_bar, buf_phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (elect_one()) {
+          umma_f8(tmem_d, adesc, bdesc, idesc, 0u);
+          umma_f8(tmem_d, adesc + 2u, bdesc + 2u, idesc, 1u);
+          umma_f8(tmem_d, adesc + 4u, bdesc + 4u, idesc, 1u);
+          umma_f8(tmem_d, adesc + 6u, bdesc + 6u, idesc, 1u);
+          umma_commit(smem_u32(&bar_mma_done[stage]));
         }
       }
-      if (lane == 0) umma_commit(smem_u32(&bar_drain));
+      if (elect_one()) umma_commit(smem_u32(&bar_drain[buf]));
       __syncwarp();
-      mbar_wait(smem_u32(&bar_drain), 0, abort_ptr);
+      mbar_wait(smem_u32(&bar_drain[buf]), 0, abort_ptr);
     }
   } else {
     // ------------------------------------------------- promotion + store --
-    reg_alloc<224>();
+    // Draining a partial is latency-bound (barrier wake-up, TMEM load round
+    // trips), so sixteen warps share it: warp w reads TMEM lanes 32*(w%4)..
+    // and the 64 columns of column group (w-4)/4, four warps per scheduler.
+    reg_alloc<kEpiRegs>();
     const int quarter = warp & 3;
-    const int half = (warp - 4) >> 2;
+    const int cgroup = (warp - 4) >> 2;
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0;
     int buf = 0;
-    uint32_t buf_phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       int m0, n0;
       decode_tile(p, w, m0, n0);
       const int row = m0 + quarter * 32 + lane;
-      const int col_base = n0 + half * 128;
+      const int col_base = n0 + cgroup * 64;
       const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.KB;
       const float* sb_ptr = p.scale_b + static_cast<size_t>(min(col_base >> 7, p.NB - 1)) * p.KB;
-      float acc[128];
+      float2 acc[32];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
-      float scale_next = __ldg(sa_ptr) * __ldg(sb_ptr);
+      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.0f, 0.0f);
+      // Scales are fetched one K block ahead and multiplied only when used.
+      float sa_next = __ldg(sa_ptr), sb_next = __ldg(sb_ptr);
       for (int kb = 0; kb < num_kb; ++kb) {
-        const float scale = scale_next;
-        if (kb + 1 < num_kb) scale_next = __ldg(sa_ptr + kb + 1) * __ldg(sb_ptr + kb + 1);
-        ok = mbar_wait(smem_u32(&bar_part_full[buf]), buf_phase, abort_ptr);
+        const float scale = sa_next * sb_next;
+        const unsigned long long scale2 = pack_f32x2(scale, scale);
+        const int kn = min(kb + 1, num_kb - 1);
+        sa_next = __ldg(sa_ptr + kn);
+        sb_next = __ldg(sb_ptr + kn);
+        ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase, abort_ptr);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t taddr =
-            tmem_base + static_cast<uint32_t>(buf * kBlockN + half * 128) + lane_field;
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32(taddr, v0);
-        tmem_ld_32x32(taddr + 32, v1);
-        tmem_ld_wait_on(v0);
-        tmem_ld_wait_on(v1);
+            tmem_base + static_cast<uint32_t>(buf * kBlockN + cgroup * 64) + lane_field;
+        uint32_t v[32];
+        tmem_ld_32x32(taddr, v);
+        tmem_ld_wait_on(v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(v0[i]), scale, acc[i]);
-        tmem_ld_32x32(taddr + 64, v0);  // in flight while the next chunk is promoted
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(v1[i]), scale, acc[32 + i]);
-        tmem_ld_32x32(taddr + 96, v1);
-        tmem_ld_wait_on(v0);
-        tmem_ld_wait_on(v1);
-        // All four loads have landed in registers: hand the buffer back.
+        for (int i = 0; i < 16; ++i) ffma2(acc[i], v[2 * i], v[2 * i + 1], scale2);
+        tmem_ld_32x32(taddr + 32, v);
+        tmem_ld_wait_on(v);
+        // Both loads have landed in registers: hand the buffer back.
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_part_empty[buf]));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(v0[i]), scale, acc[64 + i]);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(v1[i]), scale, acc[96 + i]);
+        for (int i = 0; i < 16; ++i) ffma2(acc[16 + i], v[2 * i], v[2 * i + 1], scale2);
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
         buf ^= 1;
-        if (buf == 0) buf_phase ^= 1u;
       }
       if (!ok) break;
       if (row < p.M && col_base < p.N) {
         uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N + col_base;
-        if (vec_ok && col_base + 128 <= p.N) {
+        if (vec_ok && col_base + 64 <= p.N) {
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
+          for (int q = 0; q < 8; ++q) {
             uint4 pk;
-            pk.x = pack2<kBf16>(acc[q * 8 + 0], acc[q * 8 + 1]);
-            pk.y = pack2<kBf16>(acc[q * 8 + 2], acc[q * 8 + 3]);
-            pk.z = pack2<kBf16>(acc[q * 8 + 4], acc[q * 8 + 5]);
-            pk.w = pack2<kBf16>(acc[q * 8 + 6], acc[q * 8 + 7]);
+            pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+            pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+            pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+            pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
             *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            if (col_base + i < p.N) out_row[i] = pack1<kBf16>(acc[i]);
+          for (int i = 0; i < 32; ++i) {
+            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
           }
         }
       }
@@ -304,6 +320,13 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
   auto kernel = gemm_blockscale_kernel<kBf16>;
   static bool attr_set = false;
   if (!attr_set) {
+    // The in-kernel register hand-off assumes the launch allocation; refuse to
+    // launch if the compiler chose another one.
+    cudaFuncAttributes fa;
+    CROQ_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
+    if (fa.numRegs != kLaunchRegs)
+      return record_text_error(CROQ_ERR_UNSUPPORTED,
+                               "block-scaled kernel was built with an unexpected register count");
     CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kSmemBytes)));
     attr_set = true;

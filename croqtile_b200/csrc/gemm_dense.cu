@@ -137,14 +137,13 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
         if (!ok) break;
-        if (lane == 0) {
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          const uint32_t a_dst = smem_base + stage * kStageBytes;
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        const uint32_t a_dst = smem_base + stage * kStageBytes;
+        if (elect_one()) {
           mbar_arrive_expect_tx(full, kStageBytes);
           tma_load_2d(a_dst, &map_a, full, kb * kBlockK, t.m0);
           tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, t.n0);
         }
-        __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -175,10 +174,12 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
         if (!ok) break;
         tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t a_src = smem_base + stage * kStageBytes;
-          const uint64_t adesc = umma_desc_k_sw128(a_src);
-          const uint64_t bdesc = umma_desc_k_sw128(a_src + kABytes);
+        // Descriptors are computed by the whole warp (warp-uniform values);
+        // one elected lane issues the asynchronous instructions.
+        const uint32_t a_src = smem_base + stage * kStageBytes;
+        const uint64_t adesc = umma_desc_k_sw128(a_src);
+        const uint64_t bdesc = umma_desc_k_sw128(a_src + kABytes);
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             // +32 bytes along K inside the swizzle row = +2 in 16-byte units
@@ -186,17 +187,15 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           umma_commit(smem_u32(&bar_empty[stage]));
         }
-        __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
-      if (lane == 0) umma_commit(smem_u32(&bar_acc_full[acc]));
-      __syncwarp();
+      if (elect_one()) umma_commit(smem_u32(&bar_acc_full[acc]));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
     // Whatever was issued must retire before TMEM is released.
-    if (lane == 0) umma_commit(smem_u32(&bar_drain));
+    if (elect_one()) umma_commit(smem_u32(&bar_drain));
     __syncwarp();
     mbar_wait(smem_u32(&bar_drain), 0, abort_ptr);
   } else if (warp >= 4) {
@@ -335,15 +334,14 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
         if (!ok) break;
-        if (lane == 0) {
-          const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
-          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+        const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
+        const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+        if (elect_one()) {
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2u * kPairStageBytes);
           tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, t.m0 + static_cast<int>(rank) * 128);
           tma_load_2d_pair(a_dst + kPairABytes, &map_b, full_leader, kb * kBlockK,
                            t.n0 + static_cast<int>(rank) * 128);
         }
-        __syncwarp();
         if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -372,25 +370,23 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
         if (!ok) break;
         tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t a_src = smem_base + stage * kPairStageBytes;
-          const uint64_t adesc = umma_desc_k_sw128(a_src);
-          const uint64_t bdesc = umma_desc_k_sw128(a_src + kPairABytes);
+        const uint32_t a_src = smem_base + stage * kPairStageBytes;
+        const uint64_t adesc = umma_desc_k_sw128(a_src);
+        const uint64_t bdesc = umma_desc_k_sw128(a_src + kPairABytes);
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k)
             umma_f16_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&bar_empty[stage]), 3);   // frees the stage in both CTAs
         }
-        __syncwarp();
         if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
-      if (lane == 0) umma_commit_pair(smem_u32(&bar_acc_full[acc]), 3);
-      __syncwarp();
+      if (elect_one()) umma_commit_pair(smem_u32(&bar_acc_full[acc]), 3);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (lane == 0) umma_commit_pair(smem_u32(&bar_drain), 1);
+    if (elect_one()) umma_commit_pair(smem_u32(&bar_drain), 1);
     __syncwarp();
     mbar_wait(smem_u32(&bar_drain), 0, abort_ptr);
   } else if (warp >= 4) {
