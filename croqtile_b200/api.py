@@ -110,3 +110,110 @@ def blockscale_gemm_e4m3(lhs: torch.Tensor, scale_lhs: torch.Tensor, rhs: torch.
                                        _v2(output), _out_dtype_flag(output), _stream())
     _lib.check(rc, "croq_blockscale_gemm_e4m3")
     return output
+
+
+# ------------------------------------------------------------------ MoE path --
+
+def moe_route_topk(logits: torch.Tensor, k: int, norm_topk: bool = True) -> dict:
+    """Top-k routing on raw logits plus the stable token permutation.
+
+    Returns a dict with ``topk_idx`` s32 [T,k], ``topk_w`` f32 [T,k],
+    ``expert_counts`` s32 [E], ``expert_offsets`` s32 [E+1], ``perm_to_src`` and
+    ``src_to_perm`` s32 [T*k] (see ``croq_moe_route_topk``)."""
+    lib = _lib.load()
+    _need_cuda(logits)
+    if logits.dtype != torch.float32:
+        raise ValueError("router logits are f32")
+    T, E = logits.shape
+    dev = logits.device
+    out = dict(
+        topk_idx=torch.empty((T, k), dtype=torch.int32, device=dev),
+        topk_w=torch.empty((T, k), dtype=torch.float32, device=dev),
+        expert_counts=torch.empty((E,), dtype=torch.int32, device=dev),
+        expert_offsets=torch.empty((E + 1,), dtype=torch.int32, device=dev),
+        perm_to_src=torch.empty((T * k,), dtype=torch.int32, device=dev),
+        src_to_perm=torch.empty((T * k,), dtype=torch.int32, device=dev),
+    )
+    rc = lib.croq_moe_route_topk(_v2(logits), int(k), int(bool(norm_topk)), _v2(out["topk_idx"]),
+                                 _v2(out["topk_w"]), _v1(out["expert_counts"]),
+                                 _v1(out["expert_offsets"]), _v1(out["perm_to_src"]),
+                                 _v1(out["src_to_perm"]), _stream())
+    _lib.check(rc, "croq_moe_route_topk")
+    return out
+
+
+def moe_permute(src: torch.Tensor, perm_to_src: torch.Tensor, k: int,
+                dst: torch.Tensor | None = None) -> torch.Tensor:
+    """dst[pos,:] = src[perm_to_src[pos] // k, :] for bf16 rows."""
+    lib = _lib.load()
+    if dst is None:
+        dst = torch.empty((perm_to_src.shape[0], src.shape[1]), dtype=src.dtype, device=src.device)
+    _need_cuda(src, perm_to_src, dst)
+    rc = lib.croq_moe_permute(_v2(src), _v1(perm_to_src), int(k), _v2(dst), _stream())
+    _lib.check(rc, "croq_moe_permute")
+    return dst
+
+
+def moe_permute_quant_e4m3(src: torch.Tensor, perm_to_src: torch.Tensor, k: int):
+    """Row gather fused with the 1x128 e4m3 quantiser: returns (q, scale)."""
+    lib = _lib.load()
+    rows, H = perm_to_src.shape[0], src.shape[1]
+    q = torch.empty((rows, H), dtype=torch.float8_e4m3fn, device=src.device)
+    scale = torch.empty((rows, H // 128), dtype=torch.float32, device=src.device)
+    _need_cuda(src, perm_to_src)
+    rc = lib.croq_moe_permute_quant_e4m3(_v2(src), _v1(perm_to_src), int(k), _v2(q), _v2(scale), _stream())
+    _lib.check(rc, "croq_moe_permute_quant_e4m3")
+    return q, scale
+
+
+def quant_rows_e4m3(x: torch.Tensor):
+    """bf16 [R,H] -> (e4m3 [R,H], f32 scales [R,H/128]), scale = amax/448 per block."""
+    lib = _lib.load()
+    _need_cuda(x)
+    R, H = x.shape
+    q = torch.empty((R, H), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty((R, H // 128), dtype=torch.float32, device=x.device)
+    rc = lib.croq_quant_rows_e4m3(_v2(x), _v2(q), _v2(scale), _stream())
+    _lib.check(rc, "croq_quant_rows_e4m3")
+    return q, scale
+
+
+def moe_unpermute(y: torch.Tensor, src_to_perm: torch.Tensor, topk_w: torch.Tensor,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t,:] = sum_j topk_w[t,j] * y[src_to_perm[t*k+j], :] (bf16 in/out, fp32 sum)."""
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty((topk_w.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
+    _need_cuda(y, src_to_perm, topk_w, out)
+    rc = lib.croq_moe_unpermute(_v2(y), _v1(src_to_perm), _v2(topk_w), _v2(out), _stream())
+    _lib.check(rc, "croq_moe_unpermute")
+    return out
+
+
+def moe_grouped_gemm_e4m3(x: torch.Tensor, x_scale: torch.Tensor, w: torch.Tensor,
+                          w_scale: torch.Tensor, expert_offsets: torch.Tensor,
+                          swiglu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Block-scaled FP8 GEMM of expert-sorted rows against per-expert weights
+    w [E,N,K]; with ``swiglu`` the result is silu(h[:, :N/2]) * h[:, N/2:]."""
+    lib = _lib.load()
+    R, N = x.shape[0], w.shape[1]
+    if out is None:
+        out = torch.empty((R, N // 2 if swiglu else N), dtype=torch.bfloat16, device=x.device)
+    _need_cuda(x, x_scale, w, w_scale, expert_offsets, out)
+    rc = lib.croq_moe_grouped_gemm_e4m3(_v2(x), _v2(x_scale), _v3(w), _v3(w_scale),
+                                        _v1(expert_offsets), _v2(out), int(bool(swiglu)), _stream())
+    _lib.check(rc, "croq_moe_grouped_gemm_e4m3")
+    return out
+
+
+def moe_forward(x: torch.Tensor, logits: torch.Tensor, w13: torch.Tensor, w13_scale: torch.Tensor,
+                w2: torch.Tensor, w2_scale: torch.Tensor, k: int = 8) -> torch.Tensor:
+    """Single-GPU MoE layer: route, permute + quantise, gate/up grouped GEMM with
+    SwiGLU, re-quantise, down grouped GEMM, weighted combine.
+    x bf16 [T,H]; logits f32 [T,E]; w13 e4m3 [E,2I,H]; w2 e4m3 [E,H,I]."""
+    r = moe_route_topk(logits, k)
+    xq, xs = moe_permute_quant_e4m3(x, r["perm_to_src"], k)
+    g = moe_grouped_gemm_e4m3(xq, xs, w13, w13_scale, r["expert_offsets"], swiglu=True)
+    gq, gs = quant_rows_e4m3(g)
+    y = moe_grouped_gemm_e4m3(gq, gs, w2, w2_scale, r["expert_offsets"], swiglu=False)
+    return moe_unpermute(y, r["src_to_perm"], r["topk_w"])

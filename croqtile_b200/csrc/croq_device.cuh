@@ -281,6 +281,61 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
       : "memory");
 }
 
+// 64 consecutive columns of the calling warp's 32 lanes, waited for and
+// delivered as 32 packed register pairs (columns 2i, 2i+1 in v[i]) so that the
+// values feed fma.rn.f32x2 without repacking.
+__device__ __forceinline__ void tmem_ld_32x64_pairs(uint32_t taddr, unsigned long long (&v)[32]) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 t<64>;\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, t16, t17, t18, t19, t20, t21, t22, t23, t24, t25, t26, t27, t28, t29, t30, t31, t32, t33, t34, t35, t36, t37, t38, t39, t40, t41, t42, t43, t44, t45, t46, t47, t48, t49, t50, t51, t52, t53, t54, t55, t56, t57, t58, t59, t60, t61, t62, t63}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;\n\t"
+      "mov.b64 %0, {t0, t1};\n\t"
+      "mov.b64 %1, {t2, t3};\n\t"
+      "mov.b64 %2, {t4, t5};\n\t"
+      "mov.b64 %3, {t6, t7};\n\t"
+      "mov.b64 %4, {t8, t9};\n\t"
+      "mov.b64 %5, {t10, t11};\n\t"
+      "mov.b64 %6, {t12, t13};\n\t"
+      "mov.b64 %7, {t14, t15};\n\t"
+      "mov.b64 %8, {t16, t17};\n\t"
+      "mov.b64 %9, {t18, t19};\n\t"
+      "mov.b64 %10, {t20, t21};\n\t"
+      "mov.b64 %11, {t22, t23};\n\t"
+      "mov.b64 %12, {t24, t25};\n\t"
+      "mov.b64 %13, {t26, t27};\n\t"
+      "mov.b64 %14, {t28, t29};\n\t"
+      "mov.b64 %15, {t30, t31};\n\t"
+      "mov.b64 %16, {t32, t33};\n\t"
+      "mov.b64 %17, {t34, t35};\n\t"
+      "mov.b64 %18, {t36, t37};\n\t"
+      "mov.b64 %19, {t38, t39};\n\t"
+      "mov.b64 %20, {t40, t41};\n\t"
+      "mov.b64 %21, {t42, t43};\n\t"
+      "mov.b64 %22, {t44, t45};\n\t"
+      "mov.b64 %23, {t46, t47};\n\t"
+      "mov.b64 %24, {t48, t49};\n\t"
+      "mov.b64 %25, {t50, t51};\n\t"
+      "mov.b64 %26, {t52, t53};\n\t"
+      "mov.b64 %27, {t54, t55};\n\t"
+      "mov.b64 %28, {t56, t57};\n\t"
+      "mov.b64 %29, {t58, t59};\n\t"
+      "mov.b64 %30, {t60, t61};\n\t"
+      "mov.b64 %31, {t62, t63};\n\t"
+      "}\n"
+      : "=l"(v[0]), "=l"(v[1]), "=l"(v[2]), "=l"(v[3]), "=l"(v[4]), "=l"(v[5]), "=l"(v[6]), "=l"(v[7]), "=l"(v[8]), "=l"(v[9]), "=l"(v[10]), "=l"(v[11]), "=l"(v[12]), "=l"(v[13]), "=l"(v[14]), "=l"(v[15]), "=l"(v[16]), "=l"(v[17]), "=l"(v[18]), "=l"(v[19]), "=l"(v[20]), "=l"(v[21]), "=l"(v[22]), "=l"(v[23]), "=l"(v[24]), "=l"(v[25]), "=l"(v[26]), "=l"(v[27]), "=l"(v[28]), "=l"(v[29]), "=l"(v[30]), "=l"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// d = a * b + d on packed fp32 pairs.
+__device__ __forceinline__ void ffma2_packed(float2& d, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(a), "l"(b));
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

@@ -13,14 +13,22 @@
 // In the reference the consumer warpgroup alternates WGMMA and the CUDA-core
 // promotion, so the tensor pipe idles during every promotion. Here the two
 // run concurrently: the partial product of K block kb is written into one of
-// two 256-column TMEM buffers while sixteen epilogue warps drain the other into
+// two 256-column TMEM buffers while eight epilogue warps drain the other into
 // register accumulators with packed two-wide fp32 FMAs.
 //   warp 0      TMA producer (128x128 A tile + 256x128 B tile per stage)
 //   warps 1,3   MMA issuers (even / odd K blocks): 4 x tcgen05.mma kind::f8f6f4
 //               128x256x32 per K block, one commit
 //   warp 2      TMEM allocation
-//   warps 4-19  promotion + store; warp w reads TMEM lanes 32*(w%4).., columns
-//               64*((w-4)/4).. and keeps 64 fp32 accumulators per thread
+//   warps 4-11  promotion + store; warp w reads TMEM lanes 32*(w%4).., columns
+//               128*((w-4)/4).. and keeps 128 fp32 accumulators per thread
+//
+// The same pipeline serves the MoE grouped GEMM (croq_moe_grouped_gemm_e4m3):
+// rows are expert-sorted, each 128-row tile belongs to one expert (tile table
+// derived in shared memory from expert_offsets at kernel start), the B tile is
+// fetched from that expert's [N,K] weight through a 3-D tensor map, and the
+// optional SwiGLU epilogue interleaves 64 gate rows and 64 up rows of the
+// weight in the B tile so that one thread owns both operands of
+// silu(gate) * up. The reference has no grouped kernel.
 #include "croq_device.cuh"
 #include "croq_host.h"
 
@@ -33,14 +41,14 @@ constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // one scale block; 128 x 1 B = one swizzle row
 constexpr int kUmmaK = 32;
 constexpr int kStages = 4;
-constexpr int kThreads = 640;        // 4 control warps + 16 promotion warps
-constexpr int kEpiWarps = 16;
+constexpr int kThreads = 384;        // 4 control warps + 8 promotion warps
+constexpr int kEpiWarps = 8;
 // Register hand-off between warpgroups (setmaxnreg). A CTA can only re-assign
 // registers it owns: what the control warpgroup gives up must cover what the
 // promotion warpgroups take, or setmaxnreg.inc would wait forever.
-constexpr int kLaunchRegs = 96;   // per thread at launch: 65536 / 640, rounded down to 8
-constexpr int kCtrlRegs = 32;
-constexpr int kEpiRegs = 112;
+constexpr int kLaunchRegs = 168;  // per thread at launch: 65536 / 384, rounded down to 8
+constexpr int kCtrlRegs = 56;
+constexpr int kEpiRegs = 224;
 static_assert((kLaunchRegs - kCtrlRegs) * 128 >= (kEpiRegs - kLaunchRegs) * kEpiWarps * 32,
               "control warps do not release enough registers for the promotion warps");
 static_assert(kLaunchRegs * kThreads <= 65536, "launch allocation exceeds the register file");
@@ -51,21 +59,34 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
 constexpr int kGroupM = 16;  // M tiles per rasterisation group
 
+enum Mode : int { kDense = 0, kGrouped = 1, kGroupedSwiGLU = 2 };
+constexpr int kMaxExperts = 1024;
+
 struct BlockScaleParams {
   uint16_t* out;
   const float* scale_a;  // [M, KB]
-  const float* scale_b;  // [NB, KB]
-  int M, N, K;
-  int KB, NB;            // number of 128-wide K blocks / N blocks
+  const float* scale_b;  // dense [NB, KB]; grouped [E, NB, KB]
+  int M, N, K;           // M = rows of lhs (all experts); N = rows of one weight
+  int KB, NB;            // number of 128-wide K blocks / N blocks (per expert)
   int tiles_m, tiles_n;
-  int total_work;
+  int total_work;        // dense: exact; grouped: upper bound used for the grid
+  int out_ld;            // output row pitch in elements
+  const int* expert_offsets;  // grouped: [E+1] device array
+  int E;
   int* status;
 };
 
-// Tile order: groups of kGroupM tile rows, M fastest inside a group, so the
-// CTAs that run together share a small set of A row panels and B column
+struct Tile {
+  int m0, n0;     // first row of lhs/out; first output column (dense, grouped) or
+                  // first gate column (SwiGLU)
+  int m_end;      // rows >= m_end are not stored
+  int expert;
+};
+
+// Dense tile order: groups of kGroupM tile rows, M fastest inside a group, so
+// the CTAs that run together share a small set of A row panels and B column
 // panels in L2.
-__device__ __forceinline__ void decode_tile(const BlockScaleParams& p, int w, int& m0, int& n0) {
+__device__ __forceinline__ Tile decode_dense(const BlockScaleParams& p, int w) {
   const int per_group = kGroupM * p.tiles_n;
   const int g = w / per_group;
   const int first_m = g * kGroupM;
@@ -73,15 +94,47 @@ __device__ __forceinline__ void decode_tile(const BlockScaleParams& p, int w, in
   const int r = w - g * per_group;
   const int tn = r / rows;
   const int tm = first_m + (r - tn * rows);
-  m0 = tm * kBlockM;
-  n0 = tn * kBlockN;
+  Tile t;
+  t.m0 = tm * kBlockM;
+  t.n0 = tn * kBlockN;
+  t.m_end = p.M;
+  t.expert = 0;
+  return t;
 }
 
-template <bool kBf16>
+// Grouped tile order: expert-major, then N tile, M tile fastest, so that CTAs
+// running together read the same expert's weight panel from L2. tile_prefix[e]
+// is the number of 128-row tiles of experts before e.
+__device__ __forceinline__ Tile decode_grouped(const BlockScaleParams& p, const int* tile_prefix,
+                                               const int* offsets_s, int w, int cols_per_tile) {
+  // w = (tiles before expert e) * tiles_n + nt * tiles_of_e + mt
+  int lo = 0, hi = p.E;   // largest e with tile_prefix[e] * tiles_n <= w
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_prefix[mid] * p.tiles_n <= w) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int tiles_e = tile_prefix[e + 1] - tile_prefix[e];
+  const int r = w - tile_prefix[e] * p.tiles_n;
+  const int nt = r / tiles_e;
+  const int mt = r - nt * tiles_e;
+  Tile t;
+  t.expert = e;
+  t.m0 = offsets_s[e] + mt * kBlockM;
+  t.m_end = offsets_s[e + 1];
+  t.n0 = nt * cols_per_tile;
+  return t;
+}
+
+template <bool kBf16, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, const BlockScaleParams p) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int tile_prefix[(kMode == kDense) ? 1 : kMaxExperts + 1];
+  __shared__ int offsets_s[(kMode == kDense) ? 1 : kMaxExperts + 1];
+  // output columns one tile covers: SwiGLU pairs 128 gate with 128 up columns
+  constexpr int kTileCols = (kMode == kGroupedSwiGLU) ? kBlockN / 2 : kBlockN;
   __shared__ __align__(8) uint64_t bar_full[kStages];      // TMA data of a stage has landed
   __shared__ __align__(8) uint64_t bar_mma_done[kStages];  // the stage's MMAs retired: the
                                                            // smem stage is free AND its TMEM
@@ -95,8 +148,38 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int num_kb = p.KB;
-  const int my_tiles = (p.total_work - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                       static_cast<int>(gridDim.x);
+  int total_work = p.total_work;
+  if constexpr (kMode != kDense) {
+    // Tile table: inclusive scan of per-expert tile counts (Hillis-Steele in
+    // shared memory; E <= kMaxExperts).
+    for (int e = threadIdx.x; e <= p.E; e += kThreads) {
+      offsets_s[e] = __ldg(p.expert_offsets + e);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= p.E; e += kThreads) {
+      int tiles = 0;
+      if (e > 0) {
+        const int cnt = offsets_s[e] - offsets_s[e - 1];
+        tiles = cnt > 0 ? (cnt + kBlockM - 1) / kBlockM : 0;
+      }
+      tile_prefix[e] = tiles;   // tiles of expert e-1; prefix[0] = 0
+    }
+    __syncthreads();
+    for (int d = 1; d <= p.E; d <<= 1) {
+      int add[(kMaxExperts + kThreads) / kThreads];
+      int n = 0;
+      for (int e = threadIdx.x; e <= p.E; e += kThreads) add[n++] = (e >= d) ? tile_prefix[e - d] : 0;
+      __syncthreads();
+      n = 0;
+      for (int e = threadIdx.x; e <= p.E; e += kThreads) tile_prefix[e] += add[n++];
+      __syncthreads();
+    }
+    total_work = tile_prefix[p.E] * p.tiles_n;
+  }
+  const int my_tiles = total_work > static_cast<int>(blockIdx.x)
+      ? (total_work - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+            static_cast<int>(gridDim.x)
+      : 0;
   const int total_kb = my_tiles * num_kb;   // K blocks this CTA walks, over all its tiles
 
   if (threadIdx.x == 0) {
@@ -137,9 +220,10 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-        int m0, n0;
-        decode_tile(p, w, m0, n0);
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        Tile t;
+        if constexpr (kMode == kDense) t = decode_dense(p, w);
+        else t = decode_grouped(p, tile_prefix, offsets_s, w, kTileCols);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase ^ 1u, abort_ptr);
           if (!ok) break;
@@ -147,8 +231,21 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           if (elect_one()) {
             mbar_arrive_expect_tx(full, kStageBytes);
-            tma_load_2d(a_dst, &map_a, full, kb * kBlockK, m0);
-            tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, n0);
+            tma_load_2d(a_dst, &map_a, full, kb * kBlockK, t.m0);
+            if constexpr (kMode == kDense) {
+              tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, t.n0);
+            } else {
+              // four boxes of 64 weight rows; SwiGLU alternates gate and up rows
+              const int half_n = p.N >> 1;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int wrow = (kMode == kGroupedSwiGLU)
+                    ? t.n0 + (q >> 1) * 64 + (q & 1) * half_n
+                    : t.n0 + q * 64;
+                tma_load_3d(a_dst + kABytes + q * (kBBytes / 4), &map_b, full, kb * kBlockK, wrow,
+                            t.expert);
+              }
+            }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -196,75 +293,119 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ------------------------------------------------- promotion + store --
-    // Draining a partial is latency-bound (barrier wake-up, TMEM load round
-    // trips), so sixteen warps share it: warp w reads TMEM lanes 32*(w%4)..
-    // and the 64 columns of column group (w-4)/4, four warps per scheduler.
+    // The promotion is bound by instruction issue, so it is kept lean: per K
+    // block a warp executes two 64-column TMEM loads that deliver packed
+    // register pairs and 64 two-wide FMAs; nothing else scales with the tile.
     reg_alloc<kEpiRegs>();
     const int quarter = warp & 3;
-    const int cgroup = (warp - 4) >> 2;
-    const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const int half = (warp - 4) >> 2;
+    const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
-      int m0, n0;
-      decode_tile(p, w, m0, n0);
-      const int row = m0 + quarter * 32 + lane;
-      const int col_base = n0 + cgroup * 64;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      Tile t;
+      if constexpr (kMode == kDense) t = decode_dense(p, w);
+      else t = decode_grouped(p, tile_prefix, offsets_s, w, kTileCols);
+      const int row = t.m0 + quarter * 32 + lane;
       const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.KB;
-      const float* sb_ptr = p.scale_b + static_cast<size_t>(min(col_base >> 7, p.NB - 1)) * p.KB;
-      float2 acc[32];
+      // Weight-scale rows of this thread's two 64-column loads. Dense/grouped:
+      // both lie in the 128-block of columns n0 + half*128. SwiGLU: the first
+      // load holds gate columns n0 + half*64.., the second the matching up columns.
+      const float* sb_base = p.scale_b + static_cast<size_t>(t.expert) * p.NB * p.KB;
+      int nb0, nb1;
+      if constexpr (kMode == kGroupedSwiGLU) {
+        nb0 = (t.n0 + half * 64) >> 7;
+        nb1 = ((p.N >> 1) + t.n0 + half * 64) >> 7;
+      } else {
+        nb0 = nb1 = (t.n0 + half * 128) >> 7;
+      }
+      const float* sb0_ptr = sb_base + static_cast<size_t>(min(nb0, p.NB - 1)) * p.KB;
+      const float* sb1_ptr = sb_base + static_cast<size_t>(min(nb1, p.NB - 1)) * p.KB;
+      float2 acc[64];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.0f, 0.0f);
+      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.0f, 0.0f);
       // Scales are fetched one K block ahead and multiplied only when used.
-      float sa_next = __ldg(sa_ptr), sb_next = __ldg(sb_ptr);
+      float sa_next = __ldg(sa_ptr), sb0_next = __ldg(sb0_ptr), sb1_next = __ldg(sb1_ptr);
       for (int kb = 0; kb < num_kb; ++kb) {
-        const float scale = sa_next * sb_next;
-        const unsigned long long scale2 = pack_f32x2(scale, scale);
+        const float scale0 = sa_next * sb0_next;
+        const float scale1 = (kMode == kGroupedSwiGLU) ? sa_next * sb1_next : scale0;
+        const unsigned long long s0 = pack_f32x2(scale0, scale0);
+        const unsigned long long s1 = pack_f32x2(scale1, scale1);
         const int kn = min(kb + 1, num_kb - 1);
         sa_next = __ldg(sa_ptr + kn);
-        sb_next = __ldg(sb_ptr + kn);
+        sb0_next = __ldg(sb0_ptr + kn);
+        if constexpr (kMode == kGroupedSwiGLU) sb1_next = __ldg(sb1_ptr + kn);
         ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase, abort_ptr);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t taddr =
-            tmem_base + static_cast<uint32_t>(buf * kBlockN + cgroup * 64) + lane_field;
-        uint32_t v[32];
-        tmem_ld_32x32(taddr, v);
-        tmem_ld_wait_on(v);
+            tmem_base + static_cast<uint32_t>(buf * kBlockN + half * 128) + lane_field;
+        unsigned long long v[32];
+        tmem_ld_32x64_pairs(taddr, v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) ffma2(acc[i], v[2 * i], v[2 * i + 1], scale2);
-        tmem_ld_32x32(taddr + 32, v);
-        tmem_ld_wait_on(v);
+        for (int i = 0; i < 32; ++i) ffma2_packed(acc[i], v[i], s0);
+        tmem_ld_32x64_pairs(taddr + 64, v);
         // Both loads have landed in registers: hand the buffer back.
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_part_empty[buf]));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) ffma2(acc[16 + i], v[2 * i], v[2 * i + 1], scale2);
+        for (int i = 0; i < 32; ++i) ffma2_packed(acc[32 + i], v[i], s1);
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
         buf ^= 1;
       }
       if (!ok) break;
-      if (row < p.M && col_base < p.N) {
-        uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N + col_base;
-        if (vec_ok && col_base + 64 <= p.N) {
+      if constexpr (kMode == kGroupedSwiGLU) {
+        // out[row, n0 + half*64 + c] = silu(gate_c) * up_c, c = 0..63
+        const int col_base = t.n0 + half * 64;
+        if (row < t.m_end && col_base < (p.N >> 1)) {
+          uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            uint4 pk;
-            pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-            pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-            pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-            pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
-            *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
-          }
-        } else {
+            float r[8];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
-            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
+            for (int j = 0; j < 4; ++j) {
+              const float2 g = acc[q * 4 + j], u = acc[32 + q * 4 + j];
+              r[2 * j] = (g.x / (1.0f + expf(-g.x))) * u.x;
+              r[2 * j + 1] = (g.y / (1.0f + expf(-g.y))) * u.y;
+            }
+            if (vec_ok && col_base + q * 8 + 8 <= (p.N >> 1)) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(r[0], r[1]);
+              pk.y = pack2<kBf16>(r[2], r[3]);
+              pk.z = pack2<kBf16>(r[4], r[5]);
+              pk.w = pack2<kBf16>(r[6], r[7]);
+              *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col_base + q * 8 + j < (p.N >> 1)) out_row[q * 8 + j] = pack1<kBf16>(r[j]);
+            }
+          }
+        }
+      } else {
+        const int col_base = t.n0 + half * 128;
+        if (row < t.m_end && col_base < p.N) {
+          uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
+          if (vec_ok && col_base + 128 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+              pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+              pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+              pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+              *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+              if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
+            }
           }
         }
       }
@@ -281,6 +422,30 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
 }
 
+// Checks the register count the hand-off assumes, raises the dynamic shared
+// memory limit, launches.
+template <bool kBf16, int kMode>
+int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b, const BlockScaleParams& p,
+                  int grid, cudaStream_t stream) {
+  auto kernel = gemm_blockscale_kernel<kBf16, kMode>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    // The in-kernel register hand-off assumes the launch allocation; refuse to
+    // launch if the compiler chose another one.
+    cudaFuncAttributes fa;
+    CROQ_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
+    if (fa.numRegs != kLaunchRegs)
+      return record_text_error(CROQ_ERR_UNSUPPORTED,
+                               "block-scaled kernel was built with an unexpected register count");
+    CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytes)));
+    attr_set = true;
+  }
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
 template <bool kBf16>
 int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const croq_view2* rhs,
                       const croq_view2* scale_rhs, const croq_view2* output,
@@ -295,7 +460,7 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
     CROQ_CUDA_TRY(cudaMemsetAsync(output->ptr, 0, static_cast<size_t>(M) * N * 2, stream));
     return CROQ_OK;
   }
-  BlockScaleParams p;
+  BlockScaleParams p = {};
   p.out = static_cast<uint16_t*>(output->ptr);
   p.scale_a = static_cast<const float*>(scale_lhs->ptr);
   p.scale_b = static_cast<const float*>(scale_rhs->ptr);
@@ -307,6 +472,9 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
   const long long total = 1ll * p.tiles_m * p.tiles_n;
   if (total > 0x7FFFFFFFll) return CROQ_ERR_SHAPE;
   p.total_work = static_cast<int>(total);
+  p.out_ld = N;
+  p.expert_offsets = nullptr;
+  p.E = 1;
   p.status = st->status_dev;
 
   CUtensorMap map_a, map_b;
@@ -316,25 +484,8 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
   rc = encode_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rhs->ptr, N, K, kBlockN,
                             kBlockK);
   if (rc != CROQ_OK) return rc;
-
-  auto kernel = gemm_blockscale_kernel<kBf16>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    // The in-kernel register hand-off assumes the launch allocation; refuse to
-    // launch if the compiler chose another one.
-    cudaFuncAttributes fa;
-    CROQ_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
-    if (fa.numRegs != kLaunchRegs)
-      return record_text_error(CROQ_ERR_UNSUPPORTED,
-                               "block-scaled kernel was built with an unexpected register count");
-    CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kSmemBytes)));
-    attr_set = true;
-  }
   const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
-  CROQ_CUDA_TRY(cudaGetLastError());
-  return CROQ_OK;
+  return launch_kernel<kBf16, kDense>(map_a, map_b, p, grid, stream);
 }
 
 }  // namespace
@@ -370,4 +521,71 @@ extern "C" int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2
   return out_dtype == CROQ_DTYPE_BF16
              ? launch_blockscale<true>(lhs, scale_lhs, rhs, scale_rhs, output, s)
              : launch_blockscale<false>(lhs, scale_lhs, rhs, scale_rhs, output, s);
+}
+
+extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
+                                          const croq_view3* w, const croq_view3* w_scale,
+                                          const croq_view1* expert_offsets,
+                                          const croq_view2* out, int swiglu,
+                                          croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(x) || !view_ok(x_scale) || !view_ok(w) || !view_ok(w_scale) ||
+      !view_ok(expert_offsets) || !view_ok(out))
+    return CROQ_ERR_NULL;
+  const size_t R = x->dims[0], K = x->dims[1];
+  const size_t E = w->dims[0], N = w->dims[1];
+  if (w->dims[2] != K || E == 0 || N == 0) return CROQ_ERR_SHAPE;
+  if (E > static_cast<size_t>(kMaxExperts)) return CROQ_ERR_UNSUPPORTED;
+  if (R > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  const size_t KB = (K + 127) / 128, NB = (N + 127) / 128;
+  if (expert_offsets->dims[0] != E + 1) return CROQ_ERR_SHAPE;
+  if (x_scale->dims[0] != R || x_scale->dims[1] != KB) return CROQ_ERR_SHAPE;
+  if (w_scale->dims[0] != E || w_scale->dims[1] != NB || w_scale->dims[2] != KB) return CROQ_ERR_SHAPE;
+  const size_t out_cols = swiglu ? N / 2 : N;
+  if (swiglu && (N % 256 != 0)) return CROQ_ERR_UNSUPPORTED;  // gate/up halves of whole 128-blocks
+  if (out->dims[0] != R || out->dims[1] != out_cols) return CROQ_ERR_SHAPE;
+  if (K == 0 || K % 16 != 0) return K == 0 ? CROQ_ERR_UNSUPPORTED : CROQ_ERR_ALIGN;
+  if ((N * K) % 16 != 0) return CROQ_ERR_ALIGN;
+  if (!aligned16(x->ptr) || !aligned16(w->ptr)) return CROQ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(out->ptr) & 1u) != 0 ||
+      (reinterpret_cast<uintptr_t>(x_scale->ptr) & 3u) != 0 ||
+      (reinterpret_cast<uintptr_t>(w_scale->ptr) & 3u) != 0 ||
+      (reinterpret_cast<uintptr_t>(expert_offsets->ptr) & 3u) != 0)
+    return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (R == 0) return CROQ_OK;
+
+  BlockScaleParams p = {};
+  p.out = static_cast<uint16_t*>(out->ptr);
+  p.scale_a = static_cast<const float*>(x_scale->ptr);
+  p.scale_b = static_cast<const float*>(w_scale->ptr);
+  p.M = static_cast<int>(R);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.KB = static_cast<int>(KB);
+  p.NB = static_cast<int>(NB);
+  p.tiles_m = 0;
+  p.tiles_n = swiglu ? static_cast<int>((N / 2 + 127) / 128) : static_cast<int>((N + 255) / 256);
+  // Upper bound of the tile count (the exact one depends on the offsets on the
+  // device): every expert can add one partial tile.
+  const long long bound = (static_cast<long long>((R + 127) / 128) + static_cast<long long>(E)) * p.tiles_n;
+  if (bound > 0x7FFFFFFFll) return CROQ_ERR_SHAPE;
+  p.total_work = static_cast<int>(bound);
+  p.out_ld = static_cast<int>(out_cols);
+  p.expert_offsets = static_cast<const int*>(expert_offsets->ptr);
+  p.E = static_cast<int>(E);
+  p.status = st->status_dev;
+
+  CUtensorMap map_a, map_b;
+  rc = encode_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x->ptr, R, K, kBlockM, kBlockK);
+  if (rc != CROQ_OK) return rc;
+  rc = encode_tensor_map_3d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->ptr, E, N, K, 64, kBlockK);
+  if (rc != CROQ_OK) return rc;
+  const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  return swiglu ? launch_kernel<true, kGroupedSwiGLU>(map_a, map_b, p, grid, stream)
+                : launch_kernel<true, kGrouped>(map_a, map_b, p, grid, stream);
 }

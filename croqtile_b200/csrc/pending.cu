@@ -6,9 +6,4 @@ int croq_gemm_sp_f16(const croq_view2*, const croq_view2*, const croq_view2*, co
                      int, croq_stream) {
   return CROQ_ERR_UNSUPPORTED;
 }
-int croq_moe_grouped_gemm_e4m3(const croq_view2*, const croq_view2*, const croq_view3*,
-                               const croq_view3*, const croq_view1*, const croq_view2*, int,
-                               croq_stream) {
-  return CROQ_ERR_UNSUPPORTED;
-}
 }
