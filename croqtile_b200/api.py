@@ -112,6 +112,22 @@ def blockscale_gemm_e4m3(lhs: torch.Tensor, scale_lhs: torch.Tensor, rhs: torch.
     return output
 
 
+def gemm_sp_f16(lhs_packed: torch.Tensor, lhs_meta: torch.Tensor, rhs: torch.Tensor,
+                output: torch.Tensor | None = None) -> torch.Tensor:
+    """2:4 sparse GEMM: lhs_packed f16 [M,K/2] + lhs_meta u8 [M,K/8] (the reference's
+    host encoding) times rhs f16 [N,K]^T -> f16 [M,N], fp32 accumulation."""
+    lib = _lib.load()
+    if output is None:
+        output = torch.empty((lhs_packed.shape[0], rhs.shape[0]), dtype=torch.float16, device=rhs.device)
+    _need_cuda(lhs_packed, lhs_meta, rhs, output)
+    if lhs_packed.dtype != torch.float16 or rhs.dtype != torch.float16 or lhs_meta.dtype != torch.uint8:
+        raise ValueError("gemm_sp_f16 takes f16 values and u8 metadata")
+    rc = lib.croq_gemm_sp_f16(_v2(lhs_packed), _v2(lhs_meta), _v2(rhs), _v2(output),
+                              _out_dtype_flag(output), _stream())
+    _lib.check(rc, "croq_gemm_sp_f16")
+    return output
+
+
 # ------------------------------------------------------------------ MoE path --
 
 def moe_route_topk(logits: torch.Tensor, k: int, norm_topk: bool = True) -> dict:

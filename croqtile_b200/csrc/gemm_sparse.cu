@@ -1,0 +1,376 @@
+// 2:4 structured-sparse f16 GEMM for sm_100a.
+//
+//   output[m,n] = RN( sum_k dense(lhs_packed, lhs_meta)[m,k] * rhs[n,k] ),  fp32 accumulation
+//
+// Replaces the sparse kernels the reference emits for tests/gpu/end2end/
+// gemm_sp.co:101-290 (`mma.row.row.sp` on WGMMA.sp 64xNx32). Operands keep the
+// reference's host format (runtime/choreo.h:1539-1571): lhs_packed f16 [M,K/2]
+// holds the two kept values of every group of four K positions, lhs_meta u8
+// [M,K/8] one nibble per group (idx0 | idx1<<2, idx0 < idx1), the even group in
+// the low nibble.
+//
+// tcgen05.mma.sp reads the metadata from tensor memory: for one instruction
+// (128 rows x 32 logical K) it takes one 32-bit column in which lane
+// 16*g + 8*h + i (g = row group of 16, h = K half, i < 8) holds, in its low
+// half-word, the 16 metadata bits of row 16*g + i for K positions 16*h..16*h+15
+// and, in its high half-word, those of row 16*g + 8 + i. The nibble order inside
+// a half-word is the reference's byte order, so the repack is a gather of
+// 16-bit pieces and is done on the fly by the four epilogue warps
+// (tcgen05.st), one K chunk (up to 8192 K positions = 256 columns) at a time.
+//
+//   warp 0    TMA producer: packed A tile 128x64 (128 B rows) + two B tiles
+//             256x64 per stage of 128 logical K positions, 128B swizzle
+//   warp 1    MMA issuer: 4 x tcgen05.mma.sp kind::f16 128x256x32 per stage
+//   warp 2    TMEM allocation (256 accumulator + 256 metadata columns)
+//   warps 4-7 metadata repack before each K chunk, epilogue after the last
+#include "croq_device.cuh"
+#include "croq_host.h"
+
+namespace croq {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 128;        // logical K positions per stage (64 packed values)
+constexpr int kStages = 2;
+constexpr int kThreads = 256;
+constexpr int kTmemCols = 512;
+constexpr int kMetaCol0 = 256;      // first metadata column
+constexpr int kChunkK = 8192;       // K positions whose metadata fit 256 columns
+constexpr uint32_t kABytes = kBlockM * 64 * 2;       // 128 rows x 64 packed f16
+constexpr uint32_t kBHalfBytes = kBlockN * 64 * 2;   // 256 rows x 64 f16
+constexpr uint32_t kStageBytes = kABytes + 2 * kBHalfBytes;
+constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+constexpr int kGroupM = 16;
+
+struct SparseParams {
+  uint16_t* out;
+  const uint8_t* meta;   // [M, K/8]
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int total_work;
+  int* status;
+};
+
+__device__ __forceinline__ void decode_tile(const SparseParams& p, int w, int& m0, int& n0) {
+  const int per_group = kGroupM * p.tiles_n;
+  const int g = w / per_group;
+  const int first_m = g * kGroupM;
+  const int rows = min(kGroupM, p.tiles_m - first_m);
+  const int r = w - g * per_group;
+  const int tn = r / rows;
+  const int tm = first_m + (r - tn * rows);
+  m0 = tm * kBlockM;
+  n0 = tn * kBlockN;
+}
+
+__device__ __forceinline__ void umma_sp_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t tmem_e, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%5], %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_e)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32_x4(uint32_t taddr, uint32_t a, uint32_t b,
+                                                 uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
+               "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sparse_kernel(const __grid_constant__ CUtensorMap map_a,
+                   const __grid_constant__ CUtensorMap map_b, const SparseParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_meta_full;   // metadata of a K chunk is in TMEM
+  __shared__ __align__(8) uint64_t bar_chunk_done;  // the chunk's MMAs retired
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_chunks = (p.K + kChunkK - 1) / kChunkK;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_meta_full), 4);
+    mbar_init(smem_u32(&bar_chunk_done), 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      int m0, n0;
+      decode_tile(p, w, m0, n0);
+      const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        const uint32_t a_dst = smem_base + stage * kStageBytes;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_2d(a_dst, &map_a, full, kb * 64, m0);                       // packed columns
+          tma_load_2d(a_dst + kABytes, &map_b, full, kb * kBlockK, n0);
+          tma_load_2d(a_dst + kABytes + kBHalfBytes, &map_b, full, kb * kBlockK + 64, n0);
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 1000000ull) {
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    constexpr uint32_t idesc = umma_idesc(kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16,
+                                          kBlockM, kBlockN, /*sparse=*/true);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t meta_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      for (int c = 0; c < num_chunks && ok; ++c) {
+        const int k0 = c * kChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
+        ok = mbar_wait(smem_u32(&bar_meta_full), meta_phase, abort_ptr);
+        if (!ok) break;
+        meta_phase ^= 1u;
+        tc_fence_after_sync();
+        for (int kb = 0; kb < kb_in_chunk; ++kb) {
+          ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * kStageBytes;
+          const uint64_t adesc = umma_desc_k_sw128(a_src);
+          const uint64_t bdesc0 = umma_desc_k_sw128(a_src + kABytes);
+          const uint64_t bdesc1 = umma_desc_k_sw128(a_src + kABytes + kBHalfBytes);
+          const uint32_t tmem_e = tmem_base + static_cast<uint32_t>(kMetaCol0 + 4 * kb);
+          if (elect_one()) {
+            // step s: 32 logical K = 16 packed values of A (32 B) and 32 values of B (64 B)
+            umma_sp_f16(tmem_base, adesc, bdesc0, tmem_e, idesc, (c | kb) != 0 ? 1u : 0u);
+            umma_sp_f16(tmem_base, adesc + 2u, bdesc0 + 4u, tmem_e + 1u, idesc, 1u);
+            umma_sp_f16(tmem_base, adesc + 4u, bdesc1, tmem_e + 2u, idesc, 1u);
+            umma_sp_f16(tmem_base, adesc + 6u, bdesc1 + 4u, tmem_e + 3u, idesc, 1u);
+            umma_commit(smem_u32(&bar_empty[stage]));
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (elect_one()) umma_commit(smem_u32(&bar_chunk_done));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------ metadata repack + epilogue --
+    const int quarter = warp & 3;
+    const int dp = quarter * 32 + lane;            // TMEM lane this thread writes / reads
+    const int row_lo_in_tile = (dp >> 4) * 16 + (dp & 7);
+    const int khalf = (dp >> 3) & 1;
+    const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const size_t meta_pitch = static_cast<size_t>(p.K) / 8;
+    uint32_t done_phase = 0;
+    bool pending = false;        // a chunk is in flight whose completion was not awaited yet
+    bool ok = true;
+    int prev_m0 = 0, prev_n0 = 0;
+    bool have_prev_tile = false;
+
+    auto epilogue = [&](int m0, int n0) {
+      const int row = m0 + dp;
+      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+      for (int cc = 0; cc < kBlockN / 32; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + lane_field + cc * 32, v);
+        tmem_ld_wait_on(v);
+        const int col0 = n0 + cc * 32;
+        if (row < p.M && col0 < p.N) {
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+    };
+
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      int m0, n0;
+      decode_tile(p, w, m0, n0);
+      const int r_lo = m0 + row_lo_in_tile, r_hi = r_lo + 8;
+      const uint8_t* meta_lo = p.meta + static_cast<size_t>(min(r_lo, p.M - 1)) * meta_pitch;
+      const uint8_t* meta_hi = p.meta + static_cast<size_t>(min(r_hi, p.M - 1)) * meta_pitch;
+      for (int c = 0; c < num_chunks; ++c) {
+        if (pending) {
+          // the previous chunk must retire before its metadata columns (and, at
+          // a tile boundary, the accumulator) are reused
+          ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
+          if (!ok) break;
+          done_phase ^= 1u;
+          tc_fence_after_sync();
+          pending = false;
+          if (c == 0 && have_prev_tile) epilogue(prev_m0, prev_n0);
+        }
+        const int k0 = c * kChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
+        for (int kb = 0; kb < kb_in_chunk; ++kb) {
+          // 16 metadata bytes per row and stage: half-word 2*s + khalf belongs to step s
+          const size_t off = static_cast<size_t>(k0) / 8 + static_cast<size_t>(kb) * 16;
+          // K is a multiple of 64, so a row's metadata ends on an 8-byte boundary:
+          // the second half of the last stage may lie past it and reads as zero.
+          const bool first_ok = off + 8 <= meta_pitch, second_ok = off + 16 <= meta_pitch;
+          const uint2 z = make_uint2(0u, 0u);
+          const uint2 lo0 = (r_lo < p.M && first_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_lo + off)) : z;
+          const uint2 lo1 = (r_lo < p.M && second_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_lo + off + 8)) : z;
+          const uint2 hi0 = (r_hi < p.M && first_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_hi + off)) : z;
+          const uint2 hi1 = (r_hi < p.M && second_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_hi + off + 8)) : z;
+          const uint32_t l[4] = {lo0.x, lo0.y, lo1.x, lo1.y}, h[4] = {hi0.x, hi0.y, hi1.x, hi1.y};
+          uint32_t wd[4];
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t lo16 = khalf ? (l[s] >> 16) : (l[s] & 0xFFFFu);
+            const uint32_t hi16 = khalf ? (h[s] >> 16) : (h[s] & 0xFFFFu);
+            wd[s] = lo16 | (hi16 << 16);
+          }
+          tmem_st_32x32_x4(tmem_base + lane_field + static_cast<uint32_t>(kMetaCol0 + 4 * kb), wd[0],
+                           wd[1], wd[2], wd[3]);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_meta_full));
+        pending = true;
+      }
+      prev_m0 = m0;
+      prev_n0 = n0;
+      have_prev_tile = true;
+    }
+    if (ok && pending) {
+      ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
+      if (ok) {
+        tc_fence_after_sync();
+        if (have_prev_tile) epilogue(prev_m0, prev_n0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+}
+
+template <bool kBf16>
+int launch_sparse(const croq_view2* lhs_packed, const croq_view2* lhs_meta, const croq_view2* rhs,
+                  const croq_view2* output, cudaStream_t stream) {
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  const int M = static_cast<int>(lhs_packed->dims[0]);
+  const int K = static_cast<int>(rhs->dims[1]);
+  const int N = static_cast<int>(rhs->dims[0]);
+  SparseParams p = {};
+  p.out = static_cast<uint16_t*>(output->ptr);
+  p.meta = static_cast<const uint8_t*>(lhs_meta->ptr);
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + kBlockM - 1) / kBlockM;
+  p.tiles_n = (N + kBlockN - 1) / kBlockN;
+  const long long total = 1ll * p.tiles_m * p.tiles_n;
+  if (total > 0x7FFFFFFFll) return CROQ_ERR_SHAPE;
+  p.total_work = static_cast<int>(total);
+  p.status = st->status_dev;
+  const CUtensorMapDataType dt =
+      kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_a, map_b;
+  rc = encode_tensor_map_2d(&map_a, dt, 2, lhs_packed->ptr, M, K / 2, kBlockM, 64);
+  if (rc != CROQ_OK) return rc;
+  rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, kBlockN, 64);
+  if (rc != CROQ_OK) return rc;
+  auto kernel = gemm_sparse_kernel<kBf16>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytes)));
+    attr_set = true;
+  }
+  const int grid = p.total_work < st->sm_count ? p.total_work : st->sm_count;
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+}  // namespace
+
+}  // namespace croq
+
+extern "C" int croq_gemm_sp_f16(const croq_view2* lhs_packed, const croq_view2* lhs_meta,
+                                const croq_view2* rhs, const croq_view2* output, int out_dtype,
+                                croq_stream stream) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(lhs_packed) || !view_ok(lhs_meta) || !view_ok(rhs) || !view_ok(output))
+    return CROQ_ERR_NULL;
+  const size_t M = lhs_packed->dims[0], N = rhs->dims[0], K = rhs->dims[1];
+  if (lhs_packed->dims[1] * 2 != K || lhs_meta->dims[0] != M || lhs_meta->dims[1] * 8 != K)
+    return CROQ_ERR_SHAPE;
+  if (output->dims[0] != M || output->dims[1] != N) return CROQ_ERR_SHAPE;
+  if (M == 0 || N == 0) return CROQ_ERR_SHAPE;
+  if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (out_dtype != CROQ_DTYPE_F16) return CROQ_ERR_UNSUPPORTED;   // operands and output are f16
+  if (K == 0 || K % 64 != 0) return CROQ_ERR_UNSUPPORTED;          // 8-byte metadata granules per row
+  if (!aligned16(lhs_packed->ptr) || !aligned16(rhs->ptr) ||
+      (reinterpret_cast<uintptr_t>(lhs_meta->ptr) & 7u) != 0)
+    return CROQ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(output->ptr) & 1u) != 0) return CROQ_ERR_ALIGN;
+  return launch_sparse<false>(lhs_packed, lhs_meta, rhs, output, static_cast<cudaStream_t>(stream));
+}

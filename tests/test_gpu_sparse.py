@@ -1,0 +1,98 @@
+"""GPU parity of the 2:4 sparse f16 GEMM (croq_gemm_sp_f16) against the CPU
+oracle, through the C ABI. Inputs follow the reference's sparse tests
+(tests/gpu/end2end/gemm_sp.co:296-413: seed-42 structured A, B snapped away
+from zero, full compare, abs tol 0.1 for f16); the tighter bound is max
+relative error 5e-3."""
+import numpy as np
+import pytest
+import torch
+
+from croqtile_b200 import api
+from tests.gpu_util import bits_of, max_rel_err, poisoned, to_dev, to_dev_16
+
+pytestmark = pytest.mark.gpu
+
+
+def random_24(rng, M, K):
+    """Dense [M,K] fp32 with exactly two non-zeros per group of four (never zero-valued)."""
+    dense = np.zeros((M, K // 4, 4), np.float32)
+    for pos in range(2):
+        pass
+    idx = np.argsort(rng.random((M, K // 4, 4)), axis=-1)[..., :2]
+    vals = (rng.random((M, K // 4, 2)) * 2 - 1).astype(np.float32)
+    vals[np.abs(vals) < 1e-3] = 0.5
+    np.put_along_axis(dense, idx, vals, axis=-1)
+    return dense.reshape(M, K)
+
+
+def run(oracle, dense_f32, rhs_f32):
+    bits = oracle.f32_to_f16(dense_f32)
+    packed, meta = oracle.sparse24_encode(bits)
+    rb = oracle.f32_to_f16(rhs_f32)
+    out = poisoned((bits.shape[0], rb.shape[0]), "f16")
+    api.gemm_sp_f16(to_dev_16(packed, "f16"), to_dev(meta), to_dev_16(rb, "f16"), out)
+    api.synchronize()
+    ref = oracle.gemm_row_row(oracle.f16_to_f32(oracle.sparse24_decode(packed, meta)), oracle.f16_to_f32(rb))
+    return oracle.f16_to_f32(bits_of(out)), ref
+
+
+def test_one_hot_rows_locate_every_metadata_position(oracle):
+    """A has a single 1.0 per row at a known K position (plus a second kept slot
+    holding 0): the product must pick exactly that column of rhs."""
+    M, K, N = 128, 128, 256
+    rng = np.random.default_rng(1)
+    rhs = rng.integers(-8, 9, (N, K)).astype(np.float32)
+    for shift in range(0, K, 7):
+        dense = np.zeros((M, K), np.float32)
+        cols = (np.arange(M) * 5 + shift) % K
+        dense[np.arange(M), cols] = 1.0
+        got, ref = run(oracle, dense, rhs)
+        np.testing.assert_array_equal(got, rhs[:, cols].T)
+        np.testing.assert_array_equal(got, ref)
+
+
+def test_reference_seed42_case(oracle, golden):
+    g = golden["sparse"]
+    got, ref = run(oracle, g["dense_a"], g["rhs"])
+    assert np.abs(got - ref).max() <= 0.1                  # the reference's acceptance
+    assert max_rel_err(got, ref, floor=0.05) <= 5e-3
+
+
+@pytest.mark.parametrize("shape", [(64, 32, 64), (128, 256, 128), (200, 520, 448), (384, 384, 8192 + 256),
+                                   (1000, 776, 1024)])
+def test_random_structured_inputs(oracle, shape):
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    dense = random_24(rng, M, K)
+    rhs = (rng.random((N, K)) * 2 - 1).astype(np.float32)
+    got, ref = run(oracle, dense, rhs)
+    assert max_rel_err(got, ref, floor=0.05 * np.sqrt(K)) <= 5e-3
+
+
+def test_config4_full_size_sampled_rows(oracle):
+    """8192^3: sampled rows against the oracle and a checksum of row sums."""
+    n = 8192
+    rng = np.random.default_rng(4001)
+    rows = np.array([0, 7, 8, 15, 16, 127, 128, 4100, 8191])
+    dense_rows = random_24(rng, len(rows), n)
+    g = torch.Generator(device="cuda").manual_seed(4002)
+    rhs = (torch.rand((n, n), generator=g, device="cuda") * 2 - 1).to(torch.float16)
+    # device-side structured A: two kept values per group at random positions
+    vals = (torch.rand((n, n // 2), generator=g, device="cuda") * 2 - 1).to(torch.float16)
+    vals[vals == 0] = 1.0
+    first = torch.randint(0, 3, (n, n // 4), generator=g, device="cuda")
+    gap = torch.randint(1, 4, (n, n // 4), generator=g, device="cuda")
+    second = torch.minimum(first + gap, torch.full_like(first, 3))
+    nib = (first | (second << 2)).to(torch.uint8)
+    meta = (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous()
+    # overwrite the sampled rows with host-generated ones so the oracle sees the same bits
+    bits = oracle.f32_to_f16(dense_rows)
+    p_rows, m_rows = oracle.sparse24_encode(bits)
+    vals[torch.from_numpy(rows).cuda()] = to_dev_16(p_rows, "f16")
+    meta[torch.from_numpy(rows).cuda()] = to_dev(m_rows)
+    out = api.gemm_sp_f16(vals, meta, rhs, poisoned((n, n), "f16"))
+    api.synchronize()
+    ref = oracle.gemm_row_row(oracle.f16_to_f32(bits), oracle.f16_to_f32(bits_of(rhs)), tile=(16, 256, 64))
+    got = oracle.f16_to_f32(bits_of(out[torch.from_numpy(rows).cuda()]))
+    assert max_rel_err(got, ref, floor=0.05 * np.sqrt(n)) <= 5e-3
+    assert torch.isfinite(out.float()).all()
