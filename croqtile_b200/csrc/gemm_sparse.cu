@@ -184,10 +184,12 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t tmem_e = tmem_base + static_cast<uint32_t>(kMetaCol0 + 4 * kb);
           if (elect_one()) {
             // step s: 32 logical K = 16 packed values of A (32 B) and 32 values of B (64 B)
+            // The metadata operand names an even column; bit 0 of the descriptor's
+            // selector field picks the odd column of the pair.
             umma_sp_f16(tmem_base, adesc, bdesc0, tmem_e, idesc, (c | kb) != 0 ? 1u : 0u);
-            umma_sp_f16(tmem_base, adesc + 2u, bdesc0 + 4u, tmem_e + 1u, idesc, 1u);
+            umma_sp_f16(tmem_base, adesc + 2u, bdesc0 + 4u, tmem_e, idesc | 1u, 1u);
             umma_sp_f16(tmem_base, adesc + 4u, bdesc1, tmem_e + 2u, idesc, 1u);
-            umma_sp_f16(tmem_base, adesc + 6u, bdesc1 + 4u, tmem_e + 3u, idesc, 1u);
+            umma_sp_f16(tmem_base, adesc + 6u, bdesc1 + 4u, tmem_e + 2u, idesc | 1u, 1u);
             umma_commit(smem_u32(&bar_empty[stage]));
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }

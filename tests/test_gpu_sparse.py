@@ -16,8 +16,6 @@ pytestmark = pytest.mark.gpu
 def random_24(rng, M, K):
     """Dense [M,K] fp32 with exactly two non-zeros per group of four (never zero-valued)."""
     dense = np.zeros((M, K // 4, 4), np.float32)
-    for pos in range(2):
-        pass
     idx = np.argsort(rng.random((M, K // 4, 4)), axis=-1)[..., :2]
     vals = (rng.random((M, K // 4, 2)) * 2 - 1).astype(np.float32)
     vals[np.abs(vals) < 1e-3] = 0.5
@@ -37,18 +35,32 @@ def run(oracle, dense_f32, rhs_f32):
 
 
 def test_one_hot_rows_locate_every_metadata_position(oracle):
-    """A has a single 1.0 per row at a known K position (plus a second kept slot
-    holding 0): the product must pick exactly that column of rhs."""
-    M, K, N = 128, 128, 256
+    """Each row keeps a single 1.0 at a known K position (the other kept slot
+    holds 0). Packed values and metadata are written by hand, because the
+    reference encoder only keeps groups that have exactly two non-zeros
+    (runtime/choreo.h:1553-1556). The product must pick exactly that column of
+    rhs, which checks the lane / column / nibble placement of every metadata
+    bit the tensor core reads."""
+    M, K, N = 256, 192, 256
     rng = np.random.default_rng(1)
     rhs = rng.integers(-8, 9, (N, K)).astype(np.float32)
-    for shift in range(0, K, 7):
-        dense = np.zeros((M, K), np.float32)
-        cols = (np.arange(M) * 5 + shift) % K
-        dense[np.arange(M), cols] = 1.0
-        got, ref = run(oracle, dense, rhs)
-        np.testing.assert_array_equal(got, rhs[:, cols].T)
-        np.testing.assert_array_equal(got, ref)
+    one = oracle.f32_to_f16(np.array([1.0], np.float32))[0]
+    for shift in range(0, K, 5):
+        cols = (np.arange(M) * 7 + shift) % K
+        packed = np.zeros((M, K // 2), np.uint16)
+        nib = np.full((M, K // 4), 0x4, np.uint8)        # idx (0,1) everywhere, values 0
+        grp, pos = cols // 4, cols % 4
+        other = np.where(pos == 0, 1, 0)                 # a second, different position
+        i0, i1 = np.minimum(pos, other), np.maximum(pos, other)
+        nib[np.arange(M), grp] = (i0 | (i1 << 2)).astype(np.uint8)
+        packed[np.arange(M), 2 * grp + (pos == i1)] = one
+        meta = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+        dense = oracle.f16_to_f32(oracle.sparse24_decode(packed, meta))
+        assert (dense[np.arange(M), cols] == 1.0).all() and dense.sum() == M
+        out = poisoned((M, N), "f16")
+        api.gemm_sp_f16(to_dev_16(packed, "f16"), to_dev(meta), to_dev_16(oracle.f32_to_f16(rhs), "f16"), out)
+        api.synchronize()
+        np.testing.assert_array_equal(oracle.f16_to_f32(bits_of(out)), rhs[:, cols].T)
 
 
 def test_reference_seed42_case(oracle, golden):
