@@ -50,6 +50,7 @@ SIGNATURES = {
     "croq_blockscale_gemm_e4m3": (c_int, [P2, P2, P2, P2, P2, c_int, c_void_p]),
     "croq_gemm_sp_f16": (c_int, [P2, P2, P2, P2, c_int, c_void_p]),
     "croq_moe_route_topk": (c_int, [P2, c_int, c_int, P2, P2, P1, P1, P1, P1, c_void_p]),
+    "croq_moe_route_topk_noalloc": (c_int, [P2, c_int, c_int, P2, P2, P1, P1, P1, P1, c_void_p]),
     "croq_moe_permute": (c_int, [P2, P1, c_int, P2, c_void_p]),
     "croq_moe_permute_quant_e4m3": (c_int, [P2, P1, c_int, P2, P2, c_void_p]),
     "croq_moe_unpermute": (c_int, [P2, P1, P2, P2, c_void_p]),

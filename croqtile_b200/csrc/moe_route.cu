@@ -15,6 +15,9 @@
 //                block bases), then a warp-shuffle scan over experts (offsets)
 //   perm_kernel  one warp per chunk of rows walks it in order; __match_any
 //                ranks rows of equal expert inside a 32-row group
+#include <mutex>
+#include <stdio.h>
+
 #include "croq_device.cuh"
 #include "croq_host.h"
 
@@ -255,5 +258,110 @@ extern "C" int croq_moe_route_topk(const croq_view2* logits, int k, int norm_top
   cudaError_t free_err = cudaFreeAsync(block_counts, stream);
   if (err != cudaSuccess) return record_cuda_error(err, "moe routing launch");
   if (free_err != cudaSuccess) return record_cuda_error(free_err, "cudaFreeAsync");
+  return CROQ_OK;
+}
+
+// ------------------------------------------------- allocation-free variant --
+// Routing for callers that must not allocate device memory at call time:
+// real-time serving loops whose memory is budgeted up front, hosts that embed
+// the library under a framework allocator they are not allowed to bypass, and
+// restricted sections that may not enter the CUDA allocator. The per-CTA expert
+// histograms that croq_moe_route_topk takes from the stream-ordered allocator
+// live here in a fixed array inside the library image instead, so every GPU
+// that loads the library carries kNoAllocScratchInts * 4 bytes (256 KiB) of it
+// until the process exits.
+constexpr int kNoAllocScratchInts = 65536;   // ceil(T/64) * E may not exceed this
+static __device__ __align__(256) int g_route_scratch[kNoAllocScratchInts];
+static __device__ __align__(256) int g_route_scratch_status[64];
+
+namespace croq {
+namespace {
+// Device address of g_route_scratch per device ordinal. The array's name is a
+// host-side handle, not a device pointer: the address is looked up once per
+// device, with that device current, and cached.
+std::mutex g_noalloc_mutex;
+int* g_noalloc_scratch_ptr[64] = {};
+int* g_noalloc_status_ptr[64] = {};
+}  // namespace
+}  // namespace croq
+
+extern "C" int croq_moe_route_topk_noalloc(const croq_view2* logits, int k, int norm_topk,
+                                           const croq_view2* topk_idx, const croq_view2* topk_w,
+                                           const croq_view1* expert_counts,
+                                           const croq_view1* expert_offsets,
+                                           const croq_view1* perm_to_src,
+                                           const croq_view1* src_to_perm, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(logits) || !view_ok(topk_idx) || !view_ok(topk_w) || !view_ok(expert_counts) ||
+      !view_ok(expert_offsets) || !view_ok(perm_to_src) || !view_ok(src_to_perm))
+    return CROQ_ERR_NULL;
+  const size_t T = logits->dims[0], E = logits->dims[1];
+  if (k <= 0 || k > 32 || static_cast<size_t>(k) > E) return CROQ_ERR_SHAPE;
+  if (E == 0 || E > kMaxExperts) return CROQ_ERR_UNSUPPORTED;
+  if (T * static_cast<size_t>(k) > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (topk_idx->dims[0] != T || topk_idx->dims[1] != static_cast<size_t>(k)) return CROQ_ERR_SHAPE;
+  if (topk_w->dims[0] != T || topk_w->dims[1] != static_cast<size_t>(k)) return CROQ_ERR_SHAPE;
+  if (expert_counts->dims[0] != E || expert_offsets->dims[0] != E + 1) return CROQ_ERR_SHAPE;
+  if (perm_to_src->dims[0] != T * k || src_to_perm->dims[0] != T * k) return CROQ_ERR_SHAPE;
+  const size_t num_blocks = (T + kTokensPerBlock - 1) / kTokensPerBlock;
+  if (num_blocks * E > static_cast<size_t>(kNoAllocScratchInts)) {
+    char text[200];
+    snprintf(text, sizeof(text),
+             "croq_moe_route_topk_noalloc: ceil(T/64)*E = %zu exceeds the built-in scratch of %d "
+             "entries (e.g. T <= 16384 at E = 256); use croq_moe_route_topk",
+             num_blocks * E, kNoAllocScratchInts);
+    return record_text_error(CROQ_ERR_UNSUPPORTED, text);
+  }
+  int dev = -1;
+  CROQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return record_text_error(CROQ_ERR_NO_DEVICE, "device ordinal out of range");
+  int* scratch = nullptr;
+  int* status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_scratch_ptr[dev] == nullptr) {
+      // First call on this device: resolve the array's device address. This
+      // first call should come before any stream capture begins.
+      void* p0 = nullptr;
+      void* p1 = nullptr;
+      CROQ_CUDA_TRY(cudaGetSymbolAddress(&p0, g_route_scratch));
+      CROQ_CUDA_TRY(cudaGetSymbolAddress(&p1, g_route_scratch_status));
+      g_noalloc_scratch_ptr[dev] = static_cast<int*>(p0);
+      g_noalloc_status_ptr[dev] = static_cast<int*>(p1);
+    }
+    scratch = g_noalloc_scratch_ptr[dev];
+    status = g_noalloc_status_ptr[dev];
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int* counts = static_cast<int*>(expert_counts->ptr);
+  int* offsets = static_cast<int*>(expert_offsets->ptr);
+  if (T == 0) {
+    CROQ_CUDA_TRY(cudaMemsetAsync(counts, 0, E * sizeof(int), stream));
+    CROQ_CUDA_TRY(cudaMemsetAsync(offsets, 0, (E + 1) * sizeof(int), stream));
+    return CROQ_OK;
+  }
+  const float* lg = static_cast<const float*>(logits->ptr);
+  int* idx = static_cast<int*>(topk_idx->ptr);
+  float* w = static_cast<float*>(topk_w->ptr);
+  const int Ti = static_cast<int>(T), Ei = static_cast<int>(E), nb = static_cast<int>(num_blocks);
+  const dim3 block(kWarpsPerBlock * 32);
+  // Nothing in the scratch has to start at zero: the top-k kernel overwrites
+  // all E entries of every histogram row that the scan and the permutation
+  // kernel read afterwards.
+  if (E <= 256)
+    moe_topk_kernel<8><<<nb, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, scratch);
+  else if (E <= 512)
+    moe_topk_kernel<16><<<nb, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, scratch);
+  else
+    moe_topk_kernel<32><<<nb, block, 0, stream>>>(lg, Ti, Ei, k, norm_topk, idx, w, scratch);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(scratch, nb, Ei, counts, offsets);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  moe_perm_kernel<<<nb, 32, 0, stream>>>(idx, scratch, offsets, static_cast<int>(T * k),
+                                         kTokensPerBlock * k, Ei,
+                                         static_cast<int*>(perm_to_src->ptr),
+                                         static_cast<int*>(src_to_perm->ptr), status);
+  CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

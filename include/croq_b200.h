@@ -128,6 +128,39 @@ int croq_moe_route_topk(const croq_view2* logits, int k, int norm_topk,
                         const croq_view1* perm_to_src, const croq_view1* src_to_perm,
                         croq_stream stream);
 
+/* croq_moe_route_topk for callers that cannot allocate device memory when they
+ * make the call. Which callers: latency-critical serving loops whose device
+ * memory is fully budgeted before they start (an allocation there can fail or
+ * stall the loop), applications that run the library under a framework-owned
+ * memory pool they must not bypass, and code in restricted sections where
+ * entering the CUDA allocator is not permitted. The regular entry point
+ * borrows a temporary buffer (one expert histogram per group of 64 tokens) from
+ * CUDA's stream-ordered allocator on every call; this one keeps that buffer as
+ * a fixed 256 KiB array inside the library image, so each GPU that loads the
+ * library holds 256 KiB for it until the process ends, and the call performs
+ * no cudaMalloc / cudaFree / pool operation of any kind.
+ *  - Arguments, results and status codes are those of croq_moe_route_topk; the
+ *    outputs are bit-identical to it.
+ *  - Limit: ceil(T/64) * E <= 65536 (for example T <= 16384 tokens at E = 256
+ *    experts). Larger problems return CROQ_ERR_UNSUPPORTED with an explanatory
+ *    croq_last_error_string(); nothing is launched.
+ *  - The first call on each device looks up the device address of the built-in
+ *    array (cudaGetSymbolAddress). Make that first call before any stream
+ *    capture begins; later calls only launch kernels.
+ *  - All calls on a device share the one array, which keeps whatever the last
+ *    call left in it. Nothing needs clearing between calls (each call rewrites
+ *    every entry it later reads), but two calls that overlap on the GPU — for
+ *    instance on two streams — race on it and give undefined results. Serialise
+ *    them, or use croq_moe_route_topk for concurrent work.
+ * This entry point has no counterpart in the reference (which has no routing
+ * code and allocates in its generated wrappers as it pleases). */
+int croq_moe_route_topk_noalloc(const croq_view2* logits, int k, int norm_topk,
+                                const croq_view2* topk_idx, const croq_view2* topk_w,
+                                const croq_view1* expert_counts,
+                                const croq_view1* expert_offsets,
+                                const croq_view1* perm_to_src, const croq_view1* src_to_perm,
+                                croq_stream stream);
+
 /* Gather rows into expert order: dst[pos,:] = src[perm_to_src[pos] / k, :].
  * src bf16 [T,H]; dst bf16 [T*k,H]. */
 int croq_moe_permute(const croq_view2* src, const croq_view1* perm_to_src, int k,

@@ -1,0 +1,92 @@
+"""croq_moe_route_topk_noalloc — the routing entry point for callers that are
+not allowed to allocate device memory when they call (the serving loop's memory
+was budgeted up front, a framework pool owns the device, or the section may
+not enter the CUDA allocator). Its temporary histograms live in a fixed array inside the
+library instead of coming from the stream-ordered allocator.
+
+The test drives the new entry point through the C ABI and requires every output
+to equal what the allocating entry point croq_moe_route_topk produces for the
+same logits: integer outputs and weights bit for bit (both run the same
+kernels). It makes two calls in a row with different logits, because all calls
+share the one built-in array and the second must not be disturbed by what the
+first left there. It also checks that the call leaves the amount of free device
+memory unchanged and that an over-sized request is refused with a message.
+
+The file name sorts last on purpose, so a run that stops at the first failure
+has already executed every other test; the test has no dependency on them and
+passes in a fresh process too.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from croqtile_b200 import _lib, api
+from croqtile_b200._lib import View1, View2
+
+pytestmark = pytest.mark.gpu
+
+OUTPUTS = ("topk_idx", "topk_w", "expert_counts", "expert_offsets", "perm_to_src", "src_to_perm")
+
+
+def v1(t):
+    return ctypes.byref(View1(t.data_ptr(), (ctypes.c_size_t * 1)(t.shape[0])))
+
+
+def v2(t):
+    return ctypes.byref(View2(t.data_ptr(), (ctypes.c_size_t * 2)(t.shape[0], t.shape[1])))
+
+
+def route_noalloc(lib, logits, k, norm_topk=1):
+    T, E = logits.shape
+    dev = logits.device
+    out = dict(
+        topk_idx=torch.full((T, k), -1, dtype=torch.int32, device=dev),
+        topk_w=torch.full((T, k), float("nan"), dtype=torch.float32, device=dev),
+        expert_counts=torch.full((E,), -1, dtype=torch.int32, device=dev),
+        expert_offsets=torch.full((E + 1,), -1, dtype=torch.int32, device=dev),
+        perm_to_src=torch.full((T * k,), -1, dtype=torch.int32, device=dev),
+        src_to_perm=torch.full((T * k,), -1, dtype=torch.int32, device=dev),
+    )
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.croq_moe_route_topk_noalloc(v2(logits), k, norm_topk, v2(out["topk_idx"]), v2(out["topk_w"]),
+                                         v1(out["expert_counts"]), v1(out["expert_offsets"]),
+                                         v1(out["perm_to_src"]), v1(out["src_to_perm"]), stream)
+    return rc, out
+
+
+def test_noalloc_routing_equals_allocating_entry_point_on_two_calls_in_a_row():
+    lib = _lib.load()
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    cases = [(16384, 256, 8), (1000, 64, 6)]          # the largest supported size, then a ragged one
+    inputs = [torch.randn((T, E), generator=gen, device="cuda") for T, E, _ in cases]
+    # two calls back to back on one stream, no synchronisation in between
+    rc1, out1 = route_noalloc(lib, inputs[0], cases[0][2])
+    rc2, out2 = route_noalloc(lib, inputs[1], cases[1][2])
+    assert rc1 == 0 and rc2 == 0, lib.croq_last_error_string()
+    api.synchronize()
+    for logits, (_, _, k), got in zip(inputs, cases, (out1, out2)):
+        want = api.moe_route_topk(logits, k)
+        api.synchronize()
+        for key in OUTPUTS:
+            assert torch.equal(got[key].view(torch.int32), want[key].view(torch.int32)), key
+
+    # a third call, now that every kernel is loaded: free device memory must not move
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    rc3, out3 = route_noalloc(lib, inputs[0], cases[0][2])
+    torch.cuda.synchronize()
+    assert rc3 == 0
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
+    for key in OUTPUTS:
+        assert torch.equal(out3[key].view(torch.int32), out1[key].view(torch.int32)), key
+
+
+def test_noalloc_routing_refuses_sizes_beyond_its_builtin_scratch():
+    lib = _lib.load()
+    logits = torch.zeros((16384 + 64, 256), dtype=torch.float32, device="cuda")   # one token group too many
+    rc, _ = route_noalloc(lib, logits, 8)
+    assert rc == 8                                                                  # CROQ_ERR_UNSUPPORTED
+    text = lib.croq_last_error_string().decode()
+    assert "65536" in text and "croq_moe_route_topk" in text
