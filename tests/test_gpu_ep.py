@@ -1,0 +1,68 @@
+"""Expert-parallel MoE on real GPUs (2 ranks, NCCL all-to-all over NVLink):
+each rank's output equals the single-GPU layer's rows for its tokens bit for
+bit. Skipped on boxes with fewer than two GPUs."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def problem(device):
+    g = torch.Generator(device=device).manual_seed(1234)
+    T, H, I, E, k = 1024, 1024, 512, 16, 4
+    x = torch.randn((T, H), generator=g, device=device).to(torch.bfloat16)
+    logits = torch.randn((T, E), generator=g, device=device)
+
+    def quant(w):
+        e, n, kk = w.shape
+        blk = w.view(e, n // 128, 128, kk // 128, 128)
+        amax = blk.abs().amax((2, 4))
+        s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+        return (blk / s[:, :, None, :, None]).view(e, n, kk).to(torch.float8_e4m3fn), s.contiguous()
+
+    w13, w13s = quant(torch.randn((E, 2 * I, H), generator=g, device=device) / H ** 0.5)
+    w2, w2s = quant(torch.randn((E, H, I), generator=g, device=device) / I ** 0.5)
+    return x, logits, w13, w13s, w2, w2s, k
+
+
+def worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from croqtile_b200 import api
+    from croqtile_b200.moe_ep import moe_forward_ep
+    x, logits, w13, w13s, w2, w2s, k = problem(torch.device("cuda", rank))   # same seed: same data on every rank
+    T, E = logits.shape
+    t_loc, e_loc = T // world, E // world
+    tok = slice(rank * t_loc, (rank + 1) * t_loc)
+    exp = slice(rank * e_loc, (rank + 1) * e_loc)
+    out = moe_forward_ep(x[tok].contiguous(), logits[tok].contiguous(), w13[exp].contiguous(),
+                         w13s[exp].contiguous(), w2[exp].contiguous(), w2s[exp].contiguous(), k=k)
+    api.synchronize()
+    np.save(Path(out_dir) / f"out_{rank}.npy", out.view(torch.int16).cpu().numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_expert_parallel_equals_single_gpu(tmp_path):
+    from croqtile_b200 import api
+    x, logits, w13, w13s, w2, w2s, k = problem(torch.device("cuda", 0))
+    full = api.moe_forward(x, logits, w13, w13s, w2, w2s, k)
+    api.synchronize()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    got = np.concatenate([np.load(tmp_path / f"out_{r}.npy") for r in range(2)])
+    np.testing.assert_array_equal(got, full.view(torch.int16).cpu().numpy())
