@@ -38,8 +38,12 @@ WORKLOADS = {
     "fp8_blockscale_8192": ("blockscale", 8192, 8192, 8192),
     "fp8_blockscale_4096x7168x7168": ("blockscale", 4096, 7168, 7168),
     "bf16_hilbert_8192": ("dense", 8192, 8192, 8192),
+    "sparse24_f16_8192": ("sparse", 8192, 8192, 8192),
+    # MoE layer, DeepSeek-V3 shape: T tokens (global), hidden, expert intermediate
+    "moe_deepseek_v3": ("moe", 16384, 7168, 2048),
 }
-NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0}
+NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0, "sparse": 4500.0, "moe": 4500.0}
+MOE_EXPERTS, MOE_TOPK = 256, 8
 
 
 def load_peaks():
@@ -238,6 +242,8 @@ def run_reference_arm(args, kind, M, N, K):
 METRIC = {
     "blockscale": "FP8 block-scaled GEMM TFLOP/s & % B200 peak",
     "dense": "persistent bf16 GEMM TFLOP/s & % B200 peak",
+    "sparse": "2:4 sparse f16 GEMM dense-equivalent TFLOP/s & % B200 sparse peak",
+    "moe": "MoE grouped-GEMM TFLOP/s @1-8 GPU",
 }
 
 
@@ -247,6 +253,8 @@ def config_of(args, kind, M, N, K):
         "M": M, "N_per_gpu": N, "N_global": N * args.gpus, "K": K,
         "inputs": ("A e4m3 [M,K] + f32 scales per 1x128, B e4m3 [N,K] + f32 scales per 128x128, out bf16; "
                    "N(0,1) sources quantised x*448/amax" if kind == "blockscale"
+                   else "A 2:4 along K as packed f16 [M,K/2] + u8 metadata [M,K/8], B f16 [N,K] uniform[-1,1), out f16"
+                   if kind == "sparse"
                    else "lhs/rhs bf16 N(0,1)/sqrt(K), Hilbert schedule over 256x256 tiles, out bf16"),
         "sharding": "right operand and output sharded along N, no collective" if args.gpus > 1 else "single GPU",
         "l2": "two operand/output sets (>= 256 MiB each) used alternately; each exceeds the 126 MB L2",
@@ -286,6 +294,18 @@ def run_croq_arm(args, kind, M, N, K):
             del b
             out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
             return dict(args=(aq, sa, bq, sb), out=out)
+        if kind == "sparse":
+            vals = (torch.rand((M, K // 2), generator=g, device=dev) * 2 - 1).to(torch.float16)
+            vals[vals == 0] = 1.0
+            first = torch.randint(0, 3, (M, K // 4), generator=g, device=dev)
+            gap = torch.randint(1, 4, (M, K // 4), generator=g, device=dev)
+            second = torch.minimum(first + gap, torch.full_like(first, 3))
+            nib = (first | (second << 2)).to(torch.uint8)
+            meta = (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous()
+            g.manual_seed(seed + 1 + 1000 * rank)
+            b = (torch.rand((N, K), generator=g, device=dev) * 2 - 1).to(torch.float16)
+            out = torch.empty((M, N), dtype=torch.float16, device=dev)
+            return dict(args=(vals, meta, b), out=out)
         a = (torch.randn((M, K), generator=g, device=dev) / K ** 0.5).to(torch.bfloat16)
         g.manual_seed(seed + 1 + 1000 * rank)
         b = (torch.randn((N, K), generator=g, device=dev) / K ** 0.5).to(torch.bfloat16)
@@ -299,6 +319,8 @@ def run_croq_arm(args, kind, M, N, K):
         s = sets[i & 1]
         if kind == "blockscale":
             api.blockscale_gemm_e4m3(*s["args"], s["out"])
+        elif kind == "sparse":
+            api.gemm_sp_f16(*s["args"], s["out"])
         else:
             api.matmul(*s["args"], s["out"], s["sched"][0], s["sched"][1], 256, 256)
 
@@ -343,6 +365,8 @@ def run_croq_arm(args, kind, M, N, K):
             d.copy_(h, non_blocking=True)
         if kind == "blockscale":
             api.blockscale_gemm_e4m3(*dev_in, s["out"])
+        elif kind == "sparse":
+            api.gemm_sp_f16(*dev_in, s["out"])
         else:
             api.matmul(*dev_in, s["out"], s["sched"][0], s["sched"][1], 256, 256)
         host_out.copy_(s["out"], non_blocking=True)
@@ -367,14 +391,14 @@ def run_croq_arm(args, kind, M, N, K):
         hbm, bf16_peak, src = load_peaks()
         # No FP8 figure is measured on this pool; the fp8 tensor rate is twice
         # the bf16 rate, so the fp8 roofline uses 2x the measured bf16 burst.
-        peak = bf16_peak * (2.0 if kind == "blockscale" else 1.0)
+        peak = bf16_peak * (2.0 if kind in ("blockscale", "sparse") else 1.0)
         launch_ms = float(per_step.mean())
         achieved = flops_step_rank / (launch_ms * 1e-3) / 1e12
         line = {
             "metric": METRIC[kind], "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms_max / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "e4m3" if kind == "blockscale" else "bf16", "data": "synthetic",
+            "dtype": {"blockscale": "e4m3", "sparse": "f16"}.get(kind, "bf16"), "data": "synthetic",
             "config": config_of(args, kind, M, N, K),
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -383,16 +407,195 @@ def run_croq_arm(args, kind, M, N, K):
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": None,
-                "peak_source": (f"of {src}: " + ("2 x " if kind == "blockscale" else "") +
+                "peak_source": (f"of {src}: " + ("2 x " if kind in ("blockscale", "sparse") else "") +
                                 f"bf16 cuBLAS burst {bf16_peak} TFLOP/s"),
                 "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[kind],
                 "nominal_peak": NOMINAL_PEAK_TFLOPS[kind],
-                "kernel": "gemm_blockscale_kernel" if kind == "blockscale" else "gemm_dense_kernel",
+                "kernel": {"blockscale": "gemm_blockscale_kernel", "sparse": "gemm_sparse_kernel"}.get(
+                    kind, "gemm_dense_pair_kernel"),
                 "launch_ms_mean": launch_ms, "launch_ms_min": float(per_step.min()),
             },
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_line(kind, M, N, K)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+
+# --------------------------------------------------------------- MoE arm ---
+
+def run_moe_arm(args, T, H, I):
+    """One step = one MoE layer forward over the global token batch: routing,
+    permute + quantise, gate/up grouped GEMM with SwiGLU, re-quantise, down
+    grouped GEMM, weighted combine. Experts are split over ranks (strong
+    scaling: the global batch and the expert set are fixed)."""
+    import torch
+    import torch.distributed as dist
+    from croqtile_b200 import api
+    from croqtile_b200.moe_ep import moe_forward_ep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    E, k = MOE_EXPERTS, MOE_TOPK
+    e_loc, t_loc = E // world, T // world
+
+    def quant_weights(n, kk, seed):
+        q = torch.empty((e_loc, n, kk), dtype=torch.float8_e4m3fn, device=dev)
+        sc = torch.empty((e_loc, n // 128, kk // 128), dtype=torch.float32, device=dev)
+        g = torch.Generator(device=dev)
+        for e0 in range(0, e_loc, 8):                       # 8 experts at a time bounds the fp32 transient
+            e1 = min(e_loc, e0 + 8)
+            g.manual_seed(seed + rank * 1000 + e0)
+            w = torch.randn((e1 - e0, n, kk), generator=g, device=dev) / kk ** 0.5
+            blk = w.view(e1 - e0, n // 128, 128, kk // 128, 128)
+            amax = blk.abs().amax((2, 4))
+            s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+            q[e0:e1] = (blk / s[:, :, None, :, None]).view(e1 - e0, n, kk).to(torch.float8_e4m3fn)
+            sc[e0:e1] = s
+        return q, sc
+
+    w13, w13s = quant_weights(2 * I, H, 5003)
+    w2, w2s = quant_weights(H, I, 5004)
+    g = torch.Generator(device=dev).manual_seed(5001 + rank)
+    xs = [torch.randn((t_loc, H), generator=g, device=dev).to(torch.bfloat16) for _ in range(2)]
+    lg = [torch.randn((t_loc, E), generator=g, device=dev) for _ in range(2)]
+
+    def step(i):
+        return moe_forward_ep(xs[i & 1], lg[i & 1], w13, w13s, w2, w2s, k=k)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    api.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+    barrier()
+    api.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    flops_step = 2.0 * T * k * (2 * I * H + H * I)
+    value = flops_step * args.steps / (total_ms * 1e-3) / 1e12
+
+    # end to end: tokens and logits from pinned host memory, output back to the host
+    hx, hl = xs[0].cpu().pin_memory(), lg[0].cpu().pin_memory()
+    dx, dl = torch.empty_like(xs[0]), torch.empty_like(lg[0])
+    hout = torch.empty((t_loc, H), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        dl.copy_(hl, non_blocking=True)
+        hout.copy_(moe_forward_ep(dx, dl, w13, w13s, w2, w2s, k=k), non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step * e2e_steps / (float(te.item()) * 1e-3) / 1e12
+
+    kernels = None
+    if world == 1:
+        # per-kernel device times of one layer (CUDA events around each call)
+        def timed(fn, reps=5):
+            fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(reps):
+                out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps, out
+        rows = T * k
+        ms_route, r = timed(lambda: api.moe_route_topk(lg[0], k))
+        ms_pq, (xq, xsc) = timed(lambda: api.moe_permute_quant_e4m3(xs[0], r["perm_to_src"], k))
+        ms_g1, gact = timed(lambda: api.moe_grouped_gemm_e4m3(xq, xsc, w13, w13s, r["expert_offsets"], swiglu=True))
+        ms_q, (gq, gs) = timed(lambda: api.quant_rows_e4m3(gact))
+        ms_g2, y = timed(lambda: api.moe_grouped_gemm_e4m3(gq, gs, w2, w2s, r["expert_offsets"]))
+        ms_un, _ = timed(lambda: api.moe_unpermute(y, r["src_to_perm"], r["topk_w"]))
+        hbm = load_peaks()[0]
+
+        def bw(nbytes, ms):
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            return {"ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm}
+        kernels = {
+            "route_topk": bw(T * E * 4 + rows * 8 + (2 * E + 1) * 4 + 2 * rows * 4, ms_route),
+            "permute_quant": bw(rows * (2 * H + H + 4 * H // 128) + rows * 4, ms_pq),
+            "grouped_gemm_gate_up_swiglu": {"ms": ms_g1, "TFLOP/s": 2.0 * rows * 2 * I * H / (ms_g1 * 1e-3) / 1e12},
+            "quant_rows": bw(rows * (2 * I + I + 4 * I // 128), ms_q),
+            "grouped_gemm_down": {"ms": ms_g2, "TFLOP/s": 2.0 * rows * H * I / (ms_g2 * 1e-3) / 1e12},
+            "unpermute": bw(rows * 2 * H + T * 2 * H + rows * 8, ms_un),
+        }
+        api.synchronize()
+
+    if rank == 0:
+        hbm, bf16_peak, src = load_peaks()
+        peak = 2.0 * bf16_peak
+        line = {
+            "metric": METRIC["moe"], "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "e4m3",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "tokens_global": T, "hidden": H, "expert_intermediate": I,
+                       "experts": E, "top_k": k, "experts_per_gpu": e_loc, "tokens_per_gpu": t_loc,
+                       "parallelism": f"ep{world}: tokens data-parallel, experts owner-partitioned, "
+                                      "NCCL all-to-all dispatch/combine" if world > 1 else "single GPU",
+                       "l2": "expert weights (11.3 GB / world) stream from HBM every step; two token sets alternate"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": t_loc * (H * 2 + E * 4),
+                    "d2h_bytes_per_step": t_loc * H * 2, "steps": e2e_steps},
+            "gpu_launches": args.steps * (8 if world == 1 else 14),
+        }
+        if kernels is not None:
+            g1 = kernels["grouped_gemm_gate_up_swiglu"]
+            line["kernels"] = kernels
+            line["roofline"] = {"bound": "tensor", "achieved": g1["TFLOP/s"], "peak": peak, "unit": "TFLOP/s",
+                                "frac": g1["TFLOP/s"] / peak, "traffic": None,
+                                "kernel": "gemm_blockscale_kernel<grouped, SwiGLU>",
+                                "peak_source": f"of {src}: 2 x bf16 cuBLAS burst {bf16_peak} TFLOP/s",
+                                "frac_of_nominal": g1["TFLOP/s"] / 4500.0}
+            if not args.no_cpu_baseline:
+                from oracle import oracle as o
+                rng = np.random.default_rng(0)
+                nt = 4
+                xq_c, xs_c = o.quant_rows_e4m3(rng.standard_normal((nt * k, H)).astype(np.float32))
+                w_c, ws_c = o.quant_blocks_e4m3((rng.standard_normal((1, 2 * I, H)) / H ** 0.5).astype(np.float32))
+                off = np.array([0, nt * k], np.int32)
+                t0 = time.perf_counter()
+                o.moe_grouped_gemm_e4m3(xq_c, xs_c, w_c, ws_c, off, True)
+                dt = time.perf_counter() - t0
+                line["cpu_baseline"] = {"value": 2.0 * nt * k * 2 * I * H / dt / 1e12, "unit": "TFLOP/s",
+                                        "cores": 1, "kind": "port",
+                                        "sample": f"{nt * k} expert-sorted rows through one expert's gate/up GEMM "
+                                                  "(oracle port; the reference has no MoE code)"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -408,6 +611,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     kind, M, N, K = WORKLOADS[args.workload]
+    if kind == "moe":
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the reference has no MoE implementation to time"}), flush=True)
+            return
+        return run_moe_arm(args, M, N, K)
     if args.impl == "reference":
         run_reference_arm(args, kind, M, N, K)
     else:
