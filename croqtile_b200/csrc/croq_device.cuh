@@ -391,9 +391,13 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
 }
 
 // Arrive on a barrier that may live in the peer CTA (shared::cluster address).
+// Default semantics (release at CTA scope): a cluster-scope release would
+// first drain every global load the thread still has in flight, which costs
+// more than a thousand cycles per arrive. What the waiter must observe here
+// are tcgen05 operations, and those are ordered by
+// tcgen05.fence::before_thread_sync ahead of the arrive.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // Tile load into this CTA's shared memory whose completion is counted on a
