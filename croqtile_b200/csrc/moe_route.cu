@@ -126,7 +126,19 @@ moe_scan_kernel(int* __restrict__ block_counts, int num_blocks, int E, int* __re
     const int e = base + threadIdx.x;
     int total = 0;
     if (e < E) {
-      for (int b = 0; b < num_blocks; ++b) {
+      // eight independent loads in flight per step; the stores follow them
+      int b = 0;
+      for (; b + 8 <= num_blocks; b += 8) {
+        int c[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c[i] = block_counts[static_cast<size_t>(b + i) * E + e];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          block_counts[static_cast<size_t>(b + i) * E + e] = total;
+          total += c[i];
+        }
+      }
+      for (; b < num_blocks; ++b) {
         int* p = block_counts + static_cast<size_t>(b) * E + e;
         const int c = *p;
         *p = total;

@@ -1,0 +1,139 @@
+// libcroq_b200 — C++ shim with the reference's call shapes.
+//
+// A Croqtile `__co__` function is called from host code as
+//   name(const choreo::spanned_view<T,Rank>&..., [stream])
+// (lib/codegen.hpp:853-912; tests/gpu/end2end/wgmma_persis.co:251,307). The
+// functions below keep those names and parameter lists and forward to the C
+// ABI of croq_b200.h, so host code written against the generated symbols
+// compiles against this header instead. They are templates over the view
+// type: anything with `data()` and `shape()[i]` works — the reference's
+// choreo::spanned_view / spanned_data (include choreo.h first) or
+// croq_b200::span_view below.
+//
+// Error behaviour: the generated wrappers print and abort
+// (runtime/choreo.h:243-257). Here every function returns the croq status;
+// define CROQ_ABORT_ON_ERROR before including this header to get the
+// reference's behaviour. Like the generated wrappers, the calls block until
+// the kernel is done (cute_codegen.cpp:3748-3754) unless a stream is passed
+// to the *_async forms.
+#ifndef CROQ_B200_HPP_
+#define CROQ_B200_HPP_
+
+#include <cstddef>
+#include <cstdio>
+#include <cstdlib>
+
+#include "croq_b200.h"
+
+// (The reference's choreo.h declares `namespace croq = choreo;`, so this header
+// uses its own namespace name and can be included next to it.)
+namespace croq_b200 {
+
+// Minimal non-owning view with the layout of choreo::spanned_view<T,Rank>.
+template <class T, size_t Rank>
+struct span_view {
+  T* ptr;
+  size_t dims[Rank];
+  T* data() const { return ptr; }
+  const size_t* shape() const { return dims; }
+};
+static_assert(sizeof(span_view<float, 2>) == sizeof(croq_view2), "span_view<T,2> must match croq_view2");
+static_assert(sizeof(span_view<int, 1>) == sizeof(croq_view1), "span_view<T,1> must match croq_view1");
+
+namespace detail {
+
+template <class V>
+inline croq_view1 v1(const V& v) {
+  return croq_view1{const_cast<void*>(static_cast<const void*>(v.data())), {static_cast<size_t>(v.shape()[0])}};
+}
+template <class V>
+inline croq_view2 v2(const V& v) {
+  return croq_view2{const_cast<void*>(static_cast<const void*>(v.data())),
+                    {static_cast<size_t>(v.shape()[0]), static_cast<size_t>(v.shape()[1])}};
+}
+template <class V>
+inline croq_view3 v3(const V& v) {
+  return croq_view3{const_cast<void*>(static_cast<const void*>(v.data())),
+                    {static_cast<size_t>(v.shape()[0]), static_cast<size_t>(v.shape()[1]),
+                     static_cast<size_t>(v.shape()[2])}};
+}
+
+inline int finish(int rc, croq_stream stream, const char* what) {
+  if (rc == CROQ_OK) rc = croq_synchronize(stream);
+#ifdef CROQ_ABORT_ON_ERROR
+  if (rc != CROQ_OK) {
+    std::fprintf(stderr, "croq: %s failed: %s (%s)\n", what, croq_status_string(rc), croq_last_error_string());
+    std::abort();
+  }
+#else
+  (void)what;
+#endif
+  return rc;
+}
+
+}  // namespace detail
+
+// `__co__ void matmul_persis_hilbert_sm90(global f16 [M,K] lhs, global f16 [N,K] rhs,
+//  global f16 [M,N] output, global s32 [T] schedule_m, global s32 [T] schedule_n)`
+// (tests/gpu/end2end/wgmma_persis.co:5-33). The reference bakes its 64x128
+// schedule tile into the kernel text; here it is an argument (default: the
+// reference's).
+template <class VA, class VB, class VC, class VS>
+inline int matmul_persis_hilbert_sm90(const VA& lhs, const VB& rhs, const VC& output,
+                                      const VS& schedule_m, const VS& schedule_n,
+                                      int sched_tile_m = 64, int sched_tile_n = 128,
+                                      croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  croq_view1 sm = detail::v1(schedule_m), sn = detail::v1(schedule_n);
+  return detail::finish(croq_matmul_f16(&a, &b, &c, &sm, &sn, sched_tile_m, sched_tile_n, stream),
+                        stream, "matmul_persis_hilbert_sm90");
+}
+
+// Same kernel on bf16 operands with 256x256 schedule tiles (the benchmark configuration).
+template <class VA, class VB, class VC, class VS>
+inline int matmul_persis_hilbert_bf16(const VA& lhs, const VB& rhs, const VC& output,
+                                      const VS& schedule_m, const VS& schedule_n,
+                                      int sched_tile_m = 256, int sched_tile_n = 256,
+                                      croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  croq_view1 sm = detail::v1(schedule_m), sn = detail::v1(schedule_n);
+  return detail::finish(croq_matmul_bf16(&a, &b, &c, &sm, &sn, sched_tile_m, sched_tile_n, stream),
+                        stream, "matmul_persis_hilbert_bf16");
+}
+
+// `__co__ void matmul_f16_ws_1p3c_persis(lhs, rhs, output)` (wgmma_persis.co:35-92):
+// no schedule arguments, tiles in row-major order.
+template <class VA, class VB, class VC>
+inline int matmul_f16_ws_1p3c_persis(const VA& lhs, const VB& rhs, const VC& output,
+                                     croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  return detail::finish(croq_matmul_f16(&a, &b, &c, nullptr, nullptr, 256, 256, stream), stream,
+                        "matmul_f16_ws_1p3c_persis");
+}
+
+// `__co__ void blockscale_gemm_e4m3_ws_persis(lhs, scale_lhs, rhs, scale_rhs, output)`
+// (wgmma_persis.co:94-154); output f16 as in the reference test, or bf16.
+template <class VA, class VSA, class VB, class VSB, class VC>
+inline int blockscale_gemm_e4m3_ws_persis(const VA& lhs, const VSA& scale_lhs, const VB& rhs,
+                                          const VSB& scale_rhs, const VC& output,
+                                          int out_dtype = CROQ_DTYPE_F16,
+                                          croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), sa = detail::v2(scale_lhs), b = detail::v2(rhs),
+             sb = detail::v2(scale_rhs), c = detail::v2(output);
+  return detail::finish(croq_blockscale_gemm_e4m3(&a, &sa, &b, &sb, &c, out_dtype, stream), stream,
+                        "blockscale_gemm_e4m3_ws_persis");
+}
+
+// Sparse `__co__` kernels of tests/gpu/end2end/gemm_sp.co:101-290 with device
+// operands: (lhs_packed, lhs_meta, rhs) -> output.
+template <class VP, class VM, class VB, class VC>
+inline int gemm_sp_f16(const VP& lhs_packed, const VM& lhs_meta, const VB& rhs, const VC& output,
+                       croq_stream stream = nullptr) {
+  croq_view2 p = detail::v2(lhs_packed), m = detail::v2(lhs_meta), b = detail::v2(rhs),
+             c = detail::v2(output);
+  return detail::finish(croq_gemm_sp_f16(&p, &m, &b, &c, CROQ_DTYPE_F16, stream), stream, "gemm_sp_f16");
+}
+
+}  // namespace croq_b200
+
+#endif  // CROQ_B200_HPP_

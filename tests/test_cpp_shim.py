@@ -1,0 +1,60 @@
+"""The C++ shim header: compiles as C++17, links against libcroq_b200.so, keeps
+the reference's call shapes, and — where the reference tree is present — binds
+to the real choreo::spanned_view with identical layout. No GPU needed: the
+calls made here fail argument checks before any CUDA work."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+LIB_DIR = ROOT / "croqtile_b200"
+REF_RUNTIME = Path("/root/reference/runtime")
+
+PROGRAM = r'''
+#include <cstdio>
+%(prolog)s
+#include "croq_b200.hpp"
+
+int main() {
+  %(view_f16)s lhs{%(null_f16)s, {64, 32}}, rhs{%(null_f16)s, {64, 48}}, out{%(null_f16)s, {64, 64}};
+  %(view_s32)s sm{%(null_s32)s, {1}}, sn{%(null_s32)s, {1}};
+  // null data pointers: the entry point must answer CROQ_ERR_NULL without touching CUDA
+  int rc = croq_b200::matmul_persis_hilbert_sm90(lhs, rhs, out, sm, sn);
+  std::printf("rc=%%d %%s\n", rc, croq_status_string(rc));
+  return rc == CROQ_ERR_NULL ? 0 : 1;
+}
+'''
+
+
+def build_and_run(tmp_path, name, prolog, view_f16, view_s32, null_f16, null_s32, extra):
+    src = tmp_path / f"{name}.cpp"
+    src.write_text(PROGRAM % dict(prolog=prolog, view_f16=view_f16, view_s32=view_s32,
+                                  null_f16=null_f16, null_s32=null_s32))
+    exe = tmp_path / name
+    cmd = ["g++", "-std=c++17", "-O1", "-w", f"-I{ROOT / 'include'}", *extra, str(src), "-o", str(exe),
+           f"-L{LIB_DIR}", "-lcroq_b200", f"-Wl,-rpath,{LIB_DIR}"]
+    subprocess.run(cmd, check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "rc=1" in out.stdout
+
+
+def test_shim_with_its_own_view_type(tmp_path, croq):
+    build_and_run(tmp_path, "own", "", "croq_b200::span_view<unsigned short, 2>", "croq_b200::span_view<int, 1>",
+                  "nullptr", "nullptr", [])
+
+
+@pytest.mark.skipif(not REF_RUNTIME.is_dir(), reason="reference tree not on this machine")
+def test_shim_binds_to_reference_spanned_view(tmp_path, croq):
+    prolog = '''#include "choreo.h"
+#include "croq_b200.h"
+static_assert(sizeof(choreo::spanned_view<choreo::f16, 2>) == sizeof(croq_view2), "layout");
+static_assert(sizeof(choreo::spanned_view<choreo::s32, 1>) == sizeof(croq_view1), "layout");
+template <class T, size_t R> struct ref_view : choreo::spanned_view<T, R> {
+  ref_view(T* p, std::initializer_list<size_t> d) : choreo::spanned_view<T, R>(p, choreo::mdspan<R>(d)) {}
+};'''
+    build_and_run(tmp_path, "ref", prolog, "ref_view<choreo::f16, 2>", "ref_view<choreo::s32, 1>",
+                  "(choreo::f16*)nullptr", "(choreo::s32*)nullptr",
+                  [f"-I{REF_RUNTIME}", "-D__CHOREO_TARGET_CC__"])
