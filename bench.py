@@ -469,8 +469,18 @@ def run_moe_arm(args, T, H, I):
     xs = [torch.randn((t_loc, H), generator=g, device=dev).to(torch.bfloat16) for _ in range(2)]
     lg = [torch.randn((t_loc, E), generator=g, device=dev) for _ in range(2)]
 
+    fused = None
+    if world > 1 and args.ep == "fused":
+        from croqtile_b200.moe_ep_fused import FusedExpertParallel
+        fused = FusedExpertParallel(H, I, E, t_loc, k)
+
+    def layer(x_in, l_in, timers=None):
+        if fused is not None:
+            return fused.forward(x_in, l_in, w13, w13s, w2, w2s, timers=timers)
+        return moe_forward_ep(x_in, l_in, w13, w13s, w2, w2s, k=k, timers=timers)
+
     def step(i):
-        return moe_forward_ep(xs[i & 1], lg[i & 1], w13, w13s, w2, w2s, k=k)
+        return layer(xs[i & 1], lg[i & 1])
 
     def barrier():
         if world > 1:
@@ -505,7 +515,7 @@ def run_moe_arm(args, T, H, I):
     def e2e_step():
         dx.copy_(hx, non_blocking=True)
         dl.copy_(hl, non_blocking=True)
-        hout.copy_(moe_forward_ep(dx, dl, w13, w13s, w2, w2s, k=k), non_blocking=True)
+        hout.copy_(layer(dx, dl), non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
     e2e_step()
@@ -520,6 +530,15 @@ def run_moe_arm(args, T, H, I):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_value = flops_step * e2e_steps / (float(te.item()) * 1e-3) / 1e12
+
+    # phase breakdown of one more step on rank 0 (device time between phase marks)
+    phases = None
+    marks = []
+    layer(xs[0], lg[0], timers=marks)
+    torch.cuda.synchronize()
+    if marks:
+        phases = {name: marks[i][1].elapsed_time(ev) for i, (name, ev) in enumerate(marks[1:])}
+    barrier()
 
     kernels = None
     if world == 1:
@@ -566,14 +585,18 @@ def run_moe_arm(args, T, H, I):
             "data": "synthetic",
             "config": {"workload": args.workload, "tokens_global": T, "hidden": H, "expert_intermediate": I,
                        "experts": E, "top_k": k, "experts_per_gpu": e_loc, "tokens_per_gpu": t_loc,
-                       "parallelism": f"ep{world}: tokens data-parallel, experts owner-partitioned, "
-                                      "NCCL all-to-all dispatch/combine" if world > 1 else "single GPU",
+                       "parallelism": (f"ep{world}: tokens data-parallel, experts owner-partitioned, " +
+                                       ("dispatch/combine fused into the row kernels over NVLink peer memory"
+                                        if fused is not None else "NCCL all-to-all dispatch/combine"))
+                       if world > 1 else "single GPU",
                        "l2": "expert weights (11.3 GB / world) stream from HBM every step; two token sets alternate"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": t_loc * (H * 2 + E * 4),
                     "d2h_bytes_per_step": t_loc * H * 2, "steps": e2e_steps},
             "gpu_launches": args.steps * (8 if world == 1 else 14),
         }
+        if phases is not None:
+            line["phases_ms_rank0"] = phases
         if kernels is not None:
             g1 = kernels["grouped_gemm_gate_up_swiglu"]
             line["kernels"] = kernels
@@ -609,6 +632,8 @@ def main():
     ap.add_argument("--impl", default="croq", choices=["croq", "reference"])
     ap.add_argument("--workload", default="fp8_blockscale_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
+                    help="MoE workload at N > 1: exchange fused into the row kernels, or NCCL all-to-all")
     args = ap.parse_args()
     kind, M, N, K = WORKLOADS[args.workload]
     if kind == "moe":

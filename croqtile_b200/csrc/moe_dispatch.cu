@@ -1,0 +1,229 @@
+// Expert-parallel token exchange fused into the row kernels, over peer memory.
+//
+// With experts partitioned over GPUs, the dispatch (token rows -> owning GPU)
+// and the combine (expert outputs -> token's GPU) are the two exchange steps of
+// an MoE layer. Instead of staging rows for a library all-to-all and regrouping
+// them afterwards, the row kernels address the peers' buffers directly through
+// NVLink-mapped pointers:
+//
+//   dispatch  the gather + 1x128 e4m3 quantiser writes every row (and its
+//             scales) straight into its final, expert-sorted position in the
+//             owner's buffer with 8-byte peer stores;
+//   combine   the weighted unpermute reads each of a token's k expert outputs
+//             from the owner's buffer with 16-byte peer loads.
+//
+// Only plain loads and stores cross the link (no TMA, no multicast). Placement:
+// the owner of expert e keeps its rows expert-major and, inside one expert,
+// ordered by source rank; dest_base[e] is the row at which THIS rank's rows of
+// expert e start in the owner's buffer (derived from the all-gathered counts),
+// so expanded row r with expert e and local permuted position pos lands at
+// dest_base[e] + (pos - expert_offsets[e]). The reference has no counterpart.
+#include <cuda_fp8.h>
+
+#include "croq_device.cuh"
+#include "croq_host.h"
+
+namespace croq {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+moe_dispatch_quant_kernel(const uint16_t* __restrict__ src, const int* __restrict__ perm_to_src,
+                          const int* __restrict__ topk_idx, const int* __restrict__ expert_offsets,
+                          const int* __restrict__ dest_base,
+                          const unsigned long long* __restrict__ peer_q,
+                          const unsigned long long* __restrict__ peer_scale, int k, int T, int E,
+                          int experts_per_rank, int capacity_rows, int H, int* __restrict__ status) {
+  const int pos = blockIdx.x;
+  const int r = perm_to_src[pos];
+  const int t = r / k;
+  if (r < 0 || t >= T) {
+    if (threadIdx.x == 0) *status = kDevBadIndex;
+    return;
+  }
+  const int e = topk_idx[r];
+  if (e < 0 || e >= E) {
+    if (threadIdx.x == 0) *status = kDevBadIndex;
+    return;
+  }
+  const int owner = e / experts_per_rank;
+  const int dest_row = dest_base[e] + (pos - expert_offsets[e]);
+  if (dest_row < 0 || dest_row >= capacity_rows) {   // owner's buffer too small for this imbalance
+    if (threadIdx.x == 0) *status = kDevBadIndex;
+    return;
+  }
+  const uint4* s4 = reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * H);
+  uint2* q2 = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(peer_q[owner]) +
+                                       static_cast<size_t>(dest_row) * H);
+  float* sc = reinterpret_cast<float*>(peer_scale[owner]) + static_cast<size_t>(dest_row) * (H / 128);
+  const int chunks = H / 8;   // multiple of 16: whole 16-lane groups stay together
+  for (int c = threadIdx.x; c < chunks; c += kRowThreads) {
+    const uint4 raw = __ldg(s4 + c);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      x[2 * i] = bf16_bits_to_f32(w[i] & 0xFFFFu);
+      x[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    const unsigned group = 0xFFFFu << (threadIdx.x & 16);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group, amax, o));
+    const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+      hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[4 + i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    q2[c] = make_uint2(lo, hi);
+    if ((threadIdx.x & 15) == 0) sc[c >> 4] = scale;
+  }
+}
+
+// out[t,:] = RN_bf16( sum_j w[t,j] * y_owner(t,j)[row(t,j), :] ), ascending j.
+template <int kMaxK>
+__global__ void __launch_bounds__(kRowThreads)
+moe_combine_remote_kernel(const unsigned long long* __restrict__ peer_y,
+                          const int* __restrict__ topk_idx, const int* __restrict__ src_to_perm,
+                          const int* __restrict__ expert_offsets, const int* __restrict__ dest_base,
+                          const float* __restrict__ topk_w, int k, int E, int experts_per_rank,
+                          int capacity_rows, int H, uint16_t* __restrict__ out,
+                          int* __restrict__ status) {
+  __shared__ const uint16_t* row_s[kMaxK];
+  __shared__ float w_s[kMaxK];
+  __shared__ int bad;
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  if (threadIdx.x < k) {
+    const size_t r = static_cast<size_t>(t) * k + threadIdx.x;
+    const int e = topk_idx[r];
+    const uint16_t* ptr = nullptr;
+    if (e < 0 || e >= E) {
+      bad = 1;
+    } else {
+      const int row = dest_base[e] + (src_to_perm[r] - expert_offsets[e]);
+      if (row < 0 || row >= capacity_rows) bad = 1;
+      else ptr = reinterpret_cast<const uint16_t*>(peer_y[e / experts_per_rank]) + static_cast<size_t>(row) * H;
+    }
+    row_s[threadIdx.x] = ptr;
+    w_s[threadIdx.x] = topk_w[r];
+  }
+  __syncthreads();
+  if (bad) {
+    if (threadIdx.x == 0) *status = kDevBadIndex;
+    return;
+  }
+  uint16_t* o = out + static_cast<size_t>(t) * H;
+  for (int c = threadIdx.x; c < H / 8; c += kRowThreads) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int j = 0; j < k; ++j) {
+      // peer memory: plain (non-texture) 16-byte load
+      const uint4 raw = *(reinterpret_cast<const uint4*>(row_s[j]) + c);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      const float wj = w_s[j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] = fmaf(wj, bf16_bits_to_f32(w[i] & 0xFFFFu), acc[2 * i]);
+        acc[2 * i + 1] = fmaf(wj, bf16_bits_to_f32(w[i] >> 16), acc[2 * i + 1]);
+      }
+    }
+    uint4 pk;
+    pk.x = pack2<true>(acc[0], acc[1]);
+    pk.y = pack2<true>(acc[2], acc[3]);
+    pk.z = pack2<true>(acc[4], acc[5]);
+    pk.w = pack2<true>(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(o)[c] = pk;
+  }
+}
+
+}  // namespace
+
+}  // namespace croq
+
+extern "C" {
+
+int croq_moe_dispatch_quant_e4m3(const croq_view2* src, const croq_view1* perm_to_src,
+                                 const croq_view2* topk_idx, const croq_view1* expert_offsets,
+                                 const croq_view1* dest_base, const croq_view1* peer_q_ptrs,
+                                 const croq_view1* peer_scale_ptrs, int experts_per_rank,
+                                 int capacity_rows, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(src) || !view_ok(perm_to_src) || !view_ok(topk_idx) || !view_ok(expert_offsets) ||
+      !view_ok(dest_base) || !view_ok(peer_q_ptrs) || !view_ok(peer_scale_ptrs))
+    return CROQ_ERR_NULL;
+  const size_t T = src->dims[0], H = src->dims[1], rows = perm_to_src->dims[0];
+  const size_t k = topk_idx->dims[1], E = dest_base->dims[0], W = peer_q_ptrs->dims[0];
+  if (topk_idx->dims[0] != T || k == 0 || rows != T * k) return CROQ_ERR_SHAPE;
+  if (expert_offsets->dims[0] != E + 1 || peer_scale_ptrs->dims[0] != W) return CROQ_ERR_SHAPE;
+  if (experts_per_rank <= 0 || capacity_rows <= 0 || W * static_cast<size_t>(experts_per_rank) != E)
+    return CROQ_ERR_SHAPE;
+  if (H % 128 != 0) return CROQ_ERR_UNSUPPORTED;
+  if (rows > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (!aligned16(src->ptr)) return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (rows == 0) return CROQ_OK;
+  moe_dispatch_quant_kernel<<<static_cast<unsigned>(rows), kRowThreads, 0,
+                              static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint16_t*>(src->ptr), static_cast<const int*>(perm_to_src->ptr),
+      static_cast<const int*>(topk_idx->ptr), static_cast<const int*>(expert_offsets->ptr),
+      static_cast<const int*>(dest_base->ptr),
+      static_cast<const unsigned long long*>(peer_q_ptrs->ptr),
+      static_cast<const unsigned long long*>(peer_scale_ptrs->ptr), static_cast<int>(k),
+      static_cast<int>(T), static_cast<int>(E), experts_per_rank, capacity_rows, static_cast<int>(H),
+      st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+int croq_moe_combine_remote(const croq_view1* peer_y_ptrs, const croq_view2* topk_idx,
+                            const croq_view1* src_to_perm, const croq_view1* expert_offsets,
+                            const croq_view1* dest_base, const croq_view2* topk_w,
+                            const croq_view2* out, int experts_per_rank, int capacity_rows,
+                            croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(peer_y_ptrs) || !view_ok(topk_idx) || !view_ok(src_to_perm) ||
+      !view_ok(expert_offsets) || !view_ok(dest_base) || !view_ok(topk_w) || !view_ok(out))
+    return CROQ_ERR_NULL;
+  const size_t T = topk_idx->dims[0], k = topk_idx->dims[1], H = out->dims[1];
+  const size_t E = dest_base->dims[0], W = peer_y_ptrs->dims[0];
+  if (k == 0 || k > 32 || topk_w->dims[0] != T || topk_w->dims[1] != k) return CROQ_ERR_SHAPE;
+  if (src_to_perm->dims[0] != T * k || out->dims[0] != T || expert_offsets->dims[0] != E + 1)
+    return CROQ_ERR_SHAPE;
+  if (experts_per_rank <= 0 || capacity_rows <= 0 || W * static_cast<size_t>(experts_per_rank) != E)
+    return CROQ_ERR_SHAPE;
+  if (H % 8 != 0) return CROQ_ERR_UNSUPPORTED;
+  if (!aligned16(out->ptr)) return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (T == 0) return CROQ_OK;
+  moe_combine_remote_kernel<32><<<static_cast<unsigned>(T), kRowThreads, 0,
+                                  static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const unsigned long long*>(peer_y_ptrs->ptr),
+      static_cast<const int*>(topk_idx->ptr), static_cast<const int*>(src_to_perm->ptr),
+      static_cast<const int*>(expert_offsets->ptr), static_cast<const int*>(dest_base->ptr),
+      static_cast<const float*>(topk_w->ptr), static_cast<int>(k), static_cast<int>(E),
+      experts_per_rank, capacity_rows, static_cast<int>(H), static_cast<uint16_t*>(out->ptr),
+      st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+}  // extern "C"

@@ -83,10 +83,12 @@ __device__ __forceinline__ void quant_chunk(const uint4 raw, uint2* q_dst, float
 template <int kQuantRows>
 __global__ void __launch_bounds__(kRowThreads)
 moe_quant_rows_kernel(const uint16_t* __restrict__ src, const int* __restrict__ perm_to_src,
-                      int k, int T, int rows, int H, uint8_t* __restrict__ dst_q,
-                      float* __restrict__ dst_scale, int* __restrict__ status) {
+                      int k, int T, int rows, const int* __restrict__ valid_rows, int H,
+                      uint8_t* __restrict__ dst_q, float* __restrict__ dst_scale,
+                      int* __restrict__ status) {
   const int chunks = H / 8;   // a multiple of 16: whole 16-lane groups are active together
   const int pos0 = blockIdx.x * kQuantRows;
+  if (valid_rows != nullptr) rows = min(rows, __ldg(valid_rows));   // row count known on the device only
   const uint4* s4[kQuantRows];
   bool live[kQuantRows];
 #pragma unroll
@@ -173,7 +175,8 @@ moe_unpermute_kernel(const uint16_t* __restrict__ y, const int* __restrict__ src
 }
 
 int launch_quant(const croq_view2* src, const croq_view1* perm, int k, const croq_view2* dst_q,
-                 const croq_view2* dst_scale, croq_stream stream_) {
+                 const croq_view2* dst_scale, croq_stream stream_,
+                 const croq_view1* valid_rows = nullptr) {
   if (!view_ok(src) || !view_ok(dst_q) || !view_ok(dst_scale)) return CROQ_ERR_NULL;
   if (perm != nullptr && !view_ok(perm)) return CROQ_ERR_NULL;
   const size_t T = src->dims[0], H = src->dims[1];
@@ -195,13 +198,14 @@ int launch_quant(const croq_view2* src, const croq_view1* perm, int k, const cro
   uint8_t* qp = static_cast<uint8_t*>(dst_q->ptr);
   float* scp = static_cast<float*>(dst_scale->ptr);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int* vr = valid_rows != nullptr ? static_cast<const int*>(valid_rows->ptr) : nullptr;
   if (H / 8 <= kRowThreads)
     moe_quant_rows_kernel<4><<<static_cast<unsigned>((rows + 3) / 4), kRowThreads, 0, stream>>>(
-        sp, pp, k, static_cast<int>(T), static_cast<int>(rows), static_cast<int>(H), qp, scp,
+        sp, pp, k, static_cast<int>(T), static_cast<int>(rows), vr, static_cast<int>(H), qp, scp,
         st->status_dev);
   else
     moe_quant_rows_kernel<1><<<static_cast<unsigned>(rows), kRowThreads, 0, stream>>>(
-        sp, pp, k, static_cast<int>(T), static_cast<int>(rows), static_cast<int>(H), qp, scp,
+        sp, pp, k, static_cast<int>(T), static_cast<int>(rows), vr, static_cast<int>(H), qp, scp,
         st->status_dev);
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
@@ -247,6 +251,13 @@ int croq_quant_rows_e4m3(const croq_view2* x, const croq_view2* q, const croq_vi
                          croq_stream stream) {
   croq::clear_error();
   return croq::launch_quant(x, nullptr, 1, q, scale, stream);
+}
+
+int croq_quant_rows_e4m3_n(const croq_view2* x, const croq_view2* q, const croq_view2* scale,
+                           const croq_view1* valid_rows, croq_stream stream) {
+  croq::clear_error();
+  if (!croq::view_ok(valid_rows) || valid_rows->dims[0] < 1) return CROQ_ERR_NULL;
+  return croq::launch_quant(x, nullptr, 1, q, scale, stream, valid_rows);
 }
 
 int croq_moe_unpermute(const croq_view2* y, const croq_view1* src_to_perm,

@@ -112,19 +112,34 @@ def moe_forward_ep(x, logits, w13, w13_scale, w2, w2_scale, k: int = 8, group=No
         raise ValueError("experts must divide evenly over ranks and w13/w2 hold this rank's experts")
     dev = x.device
 
+    def mark(name):
+        """Records a device timestamp for the phase that just ended (timers is a
+        list of (name, torch.cuda.Event) pairs supplied by the caller)."""
+        if timers is not None and x.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            timers.append((name, ev))
+
+    mark("start")
     r = backend.route(logits, k)
     xq, xs = backend.permute_quant(x, r["perm_to_src"], k)
+    mark("route+permute_quant")
     if world == 1:
         offsets = r["expert_offsets"]
         g = backend.grouped_gemm(xq, xs, w13, w13_scale, offsets, True)
         gq, gs = backend.quant_rows(g)
         y = backend.grouped_gemm(gq, gs, w2, w2_scale, offsets, False)
-        return backend.unpermute(y, r["src_to_perm"], r["topk_w"])
+        mark("expert_gemms")
+        out = backend.unpermute(y, r["src_to_perm"], r["topk_w"])
+        mark("unpermute")
+        return out
 
     send_rows, recv_counts = plan_exchange(r["expert_counts"], world, rank, group)
     recv_rows = recv_counts.sum(1)
+    mark("count_exchange")
     xq_in = _all_to_all_rows(xq, send_rows, recv_rows, group)
     xs_in = _all_to_all_rows(xs, send_rows, recv_rows, group)
+    mark("dispatch_all_to_all")
 
     index_np = regroup_index(recv_counts)
     index = torch.from_numpy(index_np).to(dev)
@@ -135,9 +150,15 @@ def moe_forward_ep(x, logits, w13, w13_scale, w2, w2_scale, k: int = 8, group=No
 
     xq_sorted = backend.gather_rows(xq_in, index)
     xs_sorted = backend.gather_rows(xs_in, index)
+    mark("regroup")
     g = backend.grouped_gemm(xq_sorted, xs_sorted, w13, w13_scale, offsets, True)
     gq, gs = backend.quant_rows(g)
     y = backend.grouped_gemm(gq, gs, w2, w2_scale, offsets, False)
+    mark("expert_gemms")
     y_out = backend.gather_rows(y, inverse)                    # back to arrival order
+    mark("inverse_regroup")
     y_home = _all_to_all_rows(y_out, recv_rows, send_rows, group)
-    return backend.unpermute(y_home, r["src_to_perm"], r["topk_w"])
+    mark("combine_all_to_all")
+    out = backend.unpermute(y_home, r["src_to_perm"], r["topk_w"])
+    mark("unpermute")
+    return out

@@ -195,6 +195,39 @@ int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
 int croq_quant_rows_e4m3(const croq_view2* x, const croq_view2* q, const croq_view2* scale,
                          croq_stream stream);
 
+/* Same, for a buffer whose number of valid rows is known only on the device:
+ * rows >= valid_rows[0] (s32, device) are left untouched. */
+int croq_quant_rows_e4m3_n(const croq_view2* x, const croq_view2* q, const croq_view2* scale,
+                           const croq_view1* valid_rows, croq_stream stream);
+
+/* ---- Expert-parallel exchange fused into the row kernels (one process per
+ * GPU, peers' buffers mapped over NVLink). No counterpart in the reference.
+ * Rank r owns experts [r*experts_per_rank, (r+1)*experts_per_rank); its receive
+ * buffers hold rows expert-major and, inside an expert, by source rank.
+ * dest_base s32 [E]: row at which THIS rank's rows of expert e start in the
+ * owner's buffers; expanded row r with expert e and local permuted position
+ * pos lands at dest_base[e] + (pos - expert_offsets[e]).
+ * peer_*_ptrs u64 [world]: device array of the base addresses of every rank's
+ * buffer (this rank's own included). capacity_rows: rows each buffer holds; a
+ * row that would fall outside sets CROQ_ERR_INDEX. ---- */
+
+/* Dispatch: gather + 1x128 e4m3 quantiser (as croq_moe_permute_quant_e4m3)
+ * writing each row and its scales into the owner's q [capacity,H] e4m3 and
+ * scale [capacity,H/128] f32 buffers with peer stores. */
+int croq_moe_dispatch_quant_e4m3(const croq_view2* src, const croq_view1* perm_to_src,
+                                 const croq_view2* topk_idx, const croq_view1* expert_offsets,
+                                 const croq_view1* dest_base, const croq_view1* peer_q_ptrs,
+                                 const croq_view1* peer_scale_ptrs, int experts_per_rank,
+                                 int capacity_rows, croq_stream stream);
+
+/* Combine: weighted unpermute (as croq_moe_unpermute) reading every expert
+ * output row from the owner's y [capacity,H] bf16 buffer with peer loads. */
+int croq_moe_combine_remote(const croq_view1* peer_y_ptrs, const croq_view2* topk_idx,
+                            const croq_view1* src_to_perm, const croq_view1* expert_offsets,
+                            const croq_view1* dest_base, const croq_view2* topk_w,
+                            const croq_view2* out, int experts_per_rank, int capacity_rows,
+                            croq_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,10 +46,18 @@ def worker(rank, world, port, out_dir):
     t_loc, e_loc = T // world, E // world
     tok = slice(rank * t_loc, (rank + 1) * t_loc)
     exp = slice(rank * e_loc, (rank + 1) * e_loc)
-    out = moe_forward_ep(x[tok].contiguous(), logits[tok].contiguous(), w13[exp].contiguous(),
-                         w13s[exp].contiguous(), w2[exp].contiguous(), w2s[exp].contiguous(), k=k)
+    args = (x[tok].contiguous(), logits[tok].contiguous(), w13[exp].contiguous(),
+            w13s[exp].contiguous(), w2[exp].contiguous(), w2s[exp].contiguous())
+    out = moe_forward_ep(*args, k=k)
     api.synchronize()
     np.save(Path(out_dir) / f"out_{rank}.npy", out.view(torch.int16).cpu().numpy())
+    # same layer with the exchange fused into the row kernels over peer memory, two steps in a row
+    from croqtile_b200.moe_ep_fused import FusedExpertParallel
+    ep = FusedExpertParallel(x.shape[1], w2.shape[2], E, t_loc, k)
+    for _ in range(2):
+        fused = ep.forward(*args)
+    api.synchronize()
+    np.save(Path(out_dir) / f"fused_{rank}.npy", fused.view(torch.int16).cpu().numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -66,3 +74,5 @@ def test_two_rank_expert_parallel_equals_single_gpu(tmp_path):
     mp.spawn(worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     got = np.concatenate([np.load(tmp_path / f"out_{r}.npy") for r in range(2)])
     np.testing.assert_array_equal(got, full.view(torch.int16).cpu().numpy())
+    fused = np.concatenate([np.load(tmp_path / f"fused_{r}.npy") for r in range(2)])
+    np.testing.assert_array_equal(fused, full.view(torch.int16).cpu().numpy())
