@@ -42,6 +42,13 @@ WORKLOADS = {
     # MoE layer, DeepSeek-V3 shape: T tokens (global), hidden, expert intermediate
     "moe_deepseek_v3": ("moe", 16384, 7168, 2048),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the
+# ncu captures summarised under profiles/ (same command, same shapes)
+NCU_DRAM_TRAFFIC_BYTES = {
+    "fp8_blockscale_8192": 338.76e6 + 113.34e6,
+    "bf16_hilbert_8192": 1.1129e9 + 128.0e6,
+    "sparse24_f16_8192": 709.02e6 + 122.42e6,
+}
 NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0, "sparse": 4500.0, "moe": 4500.0}
 MOE_EXPERTS, MOE_TOPK = 256, 8
 
@@ -406,7 +413,11 @@ def run_croq_arm(args, kind, M, N, K):
             "gpu_launches": args.steps,
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(args.workload),
+                "traffic_unit": "bytes per launch (ncu dram read + write)",
+                "algorithmic_bytes": float(M * K + N * K + 2 * M * N) if kind == "blockscale" else
+                                     float(2 * (M * K + N * K + M * N)) if kind == "dense" else
+                                     float(M * K + M * K // 8 + 2 * N * K + 2 * M * N),
                 "peak_source": (f"of {src}: " + ("2 x " if kind in ("blockscale", "sparse") else "") +
                                 f"bf16 cuBLAS burst {bf16_peak} TFLOP/s"),
                 "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[kind],
