@@ -23,9 +23,6 @@ enum DeviceStatus : int {
 };
 
 // Wall-clock budget of one wait, in nanoseconds of %globaltimer.
-#ifndef CROQ_FAST_POLLS
-#define CROQ_FAST_POLLS 64
-#endif
 #ifndef CROQ_WAIT_BUDGET_NS
 #define CROQ_WAIT_BUDGET_NS 1000000000ull
 #endif
@@ -109,31 +106,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Waits for the phase with the given parity to complete. Returns false when
 // the budget ran out or another role already aborted; the caller then leaves
-// its loops and walks to the common teardown. The first polls use the
-// non-suspending test_wait (a ready barrier costs a few tens of cycles instead
-// of the ~130 a try_wait takes to come back); a long wait falls back to
-// try_wait, which parks the thread between polls.
+// its loops and walks to the common teardown. try_wait parks the thread in
+// hardware between polls; busy-polling with test_wait first was measured to
+// cost 2-3 % of GEMM throughput (issue slots and power), so it is not used.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_word) {
-#pragma unroll 1
-  for (int i = 0; i < CROQ_FAST_POLLS; ++i)
-    if (mbar_test_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   for (;;) {

@@ -29,6 +29,8 @@
 // optional SwiGLU epilogue interleaves 64 gate rows and 64 up rows of the
 // weight in the B tile so that one thread owns both operands of
 // silu(gate) * up. The reference has no grouped kernel.
+#include <stdlib.h>
+
 #include "croq_device.cuh"
 #include "croq_host.h"
 
@@ -39,7 +41,6 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // one scale block; 128 x 1 B = one swizzle row
-constexpr int kUmmaK = 32;
 constexpr int kStages = 4;
 constexpr int kThreads = 384;        // 4 control warps + 8 promotion warps
 constexpr int kEpiWarps = 8;
@@ -422,6 +423,235 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
 }
 
+// ------------------------------------------------------------ CTA-pair form --
+// Dense block-scaled GEMM on CTA pairs. All three single-CTA GEMM kernels of
+// this library run into the same wall: L2 -> SM operand traffic tops out near
+// 12-13 TB/s (measured with ncu: l1tex__m_xbar2l1tex_read_bytes), and a
+// 128x256 tile needs 48 KB of operands per K block. A pair of CTAs sharing a
+// 256x256 tile needs 32 KB per CTA for the same flops: each CTA loads its own
+// 128 rows of A and 128 rows of B (no multicast), rank 0 issues
+// tcgen05.mma.cta_group::2 (M=256, N=256), each CTA's TMEM receives its 128
+// rows of the partial, and each CTA's promotion warps drain and promote them
+// exactly as in the single-CTA form. The partial-buffer hand-back of the peer
+// CTA is a remote mbarrier arrive on the leader's barrier.
+constexpr int kPairM = 256;
+constexpr int kPairN = 256;
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairABytes = 128 * kBlockK;
+constexpr uint32_t kPairBBytes = 128 * kBlockK;
+constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+constexpr int kPairGroupM = 8;
+
+__device__ __forceinline__ void decode_pair_tile(const BlockScaleParams& p, int w, int& m0, int& n0) {
+  // tiles_m / tiles_n count 256x256 tiles here
+  const int per_group = kPairGroupM * p.tiles_n;
+  const int g = w / per_group;
+  const int first_m = g * kPairGroupM;
+  const int rows = min(kPairGroupM, p.tiles_m - first_m);
+  const int r = w - g * per_group;
+  const int tn = r / rows;
+  const int tm = first_m + (r - tn * rows);
+  m0 = tm * kPairM;
+  n0 = tn * kPairN;
+}
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                            const __grid_constant__ CUtensorMap map_b, const BlockScaleParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];       // used in rank 0
+  __shared__ __align__(8) uint64_t bar_mma_done[kPairStages];   // one per CTA (multicast commit)
+  __shared__ __align__(8) uint64_t bar_part_empty[2];           // used in rank 0
+  __shared__ __align__(8) uint64_t bar_drain[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_kb = p.KB;
+  const int my_tiles = p.total_work > pair ? (p.total_work - pair + num_pairs - 1) / num_pairs : 0;
+  const int total_kb = my_tiles * num_kb;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_mma_done[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_part_empty[b]), 2 * kEpiWarps);   // promotion warps of both CTAs
+      mbar_init(smem_u32(&bar_drain[b]), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_word;
+  ClockProbe probe;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.begin();
+
+  if (warp < 4) {
+    reg_dealloc<kCtrlRegs>();
+    if (warp == 0) {
+      // ---------------------------------------------------------- producer --
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+        int m0, n0;
+        decode_pair_tile(p, w, m0, n0);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase ^ 1u, abort_ptr);
+          if (!ok) break;
+          const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
+          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2u * kPairStageBytes);
+            tma_load_2d_pair(a_dst, &map_a, full_leader, kb * kBlockK, m0 + static_cast<int>(rank) * 128);
+            tma_load_2d_pair(a_dst + kPairABytes, &map_b, full_leader, kb * kBlockK,
+                             n0 + static_cast<int>(rank) * 128);
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 1000000ull) {
+        }
+      }
+    } else if ((warp == 1 || warp == 3) && rank == 0) {
+      // ----------------------------------------- MMA issuers (leader CTA) --
+      constexpr uint32_t idesc = umma_idesc(kFmtE4M3, kFmtE4M3, kPairM, kPairN);
+      const int buf = (warp == 1) ? 0 : 1;
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kPairN);
+      const uint32_t empty_bar = smem_u32(&bar_part_empty[buf]);
+      bool ok = true;
+      for (int g = buf; g < total_kb; g += 2) {
+        const int stage = g % kPairStages;
+        const uint32_t phase = static_cast<uint32_t>(g / kPairStages) & 1u;
+        const uint32_t buf_phase = static_cast<uint32_t>(g >> 1) & 1u;
+        const uint32_t a_src = smem_base + stage * kPairStageBytes;
+        const uint64_t adesc = umma_desc_k_sw128(a_src);
+        const uint64_t bdesc = umma_desc_k_sw128(a_src + kPairABytes);
+        ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+        if (!ok) break;
+        ok = mbar_wait(empty_bar, buf_phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (elect_one()) {
+          umma_f8_pair(tmem_d, adesc, bdesc, idesc, 0u);
+          umma_f8_pair(tmem_d, adesc + 2u, bdesc + 2u, idesc, 1u);
+          umma_f8_pair(tmem_d, adesc + 4u, bdesc + 4u, idesc, 1u);
+          umma_f8_pair(tmem_d, adesc + 6u, bdesc + 6u, idesc, 1u);
+          umma_commit_pair(smem_u32(&bar_mma_done[stage]), 3);
+        }
+      }
+      if (elect_one()) umma_commit_pair(smem_u32(&bar_drain[buf]), 1);
+      __syncwarp();
+      mbar_wait(smem_u32(&bar_drain[buf]), 0, abort_ptr);
+    }
+  } else {
+    // ------------------------------------------------- promotion + store --
+    reg_alloc<kEpiRegs>();
+    const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;
+    const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      int m0, n0;
+      decode_pair_tile(p, w, m0, n0);
+      const int row = m0 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const int col_base = n0 + half * 128;
+      const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.KB;
+      const float* sb_ptr = p.scale_b + static_cast<size_t>(min(col_base >> 7, p.NB - 1)) * p.KB;
+      float2 acc[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.0f, 0.0f);
+      float sa_next = __ldg(sa_ptr), sb_next = __ldg(sb_ptr);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const float scale = sa_next * sb_next;
+        const unsigned long long s2 = pack_f32x2(scale, scale);
+        ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t taddr =
+            tmem_base + static_cast<uint32_t>(buf * kPairN + half * 128) + lane_field;
+        unsigned long long v[32];
+        tmem_ld_32x64_pairs(taddr, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ffma2_packed(acc[i], v[i], s2);
+        tmem_ld_32x64_pairs(taddr + 64, v);
+        // Both loads have landed in registers: hand the buffer back to the
+        // leader's issuer (a remote arrive for the peer CTA).
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_part_empty[buf]), 0));
+        // next block's scales: requested after the arrive, so no global load
+        // is in flight when the arrive's release is performed
+        const int kn = min(kb + 1, num_kb - 1);
+        sa_next = __ldg(sa_ptr + kn);
+        sb_next = __ldg(sb_ptr + kn);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ffma2_packed(acc[32 + i], v[i], s2);
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        buf ^= 1;
+      }
+      if (!ok) break;
+      if (row < p.M && col_base < p.N) {
+        uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
+        if (vec_ok && col_base + 128 <= p.N) {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            uint4 pk;
+            pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+            pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+            pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+            pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+            *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
+          }
+        }
+      }
+    }
+  }
+
+  // Neither CTA may retire while its peer can still signal its barriers or the
+  // shared MMA can still touch its shared memory or TMEM.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+  if (blockIdx.x == 0 && threadIdx.x == 0) probe.end(p.status);
+}
+
 // Checks the register count the hand-off assumes, raises the dynamic shared
 // memory limit, launches.
 template <bool kBf16, int kMode>
@@ -481,6 +711,36 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
   rc = encode_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, lhs->ptr, M, K, kBlockM,
                             kBlockK);
   if (rc != CROQ_OK) return rc;
+  // CROQ_BLOCKSCALE_PAIR=0 in the environment keeps every shape on the single-CTA kernel
+  // (tuning knob; the pair kernel is the default above 128 rows).
+  static const bool pair_allowed = [] {
+    const char* e = getenv("CROQ_BLOCKSCALE_PAIR");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  if (pair_allowed && M > kBlockM && st->sm_count >= 2) {
+    // CTA pairs on 256x256 tiles: two thirds of the operand traffic per flop
+    p.tiles_m = (M + kPairM - 1) / kPairM;
+    p.tiles_n = (N + kPairN - 1) / kPairN;
+    p.total_work = p.tiles_m * p.tiles_n;
+    rc = encode_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rhs->ptr, N, K, 128, kBlockK);
+    if (rc != CROQ_OK) return rc;
+    auto kernel = gemm_blockscale_pair_kernel<kBf16>;
+    static bool pair_attr_set = false;
+    if (!pair_attr_set) {
+      cudaFuncAttributes fa;
+      CROQ_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
+      if (fa.numRegs != kLaunchRegs)
+        return record_text_error(CROQ_ERR_UNSUPPORTED,
+                                 "block-scaled pair kernel was built with an unexpected register count");
+      CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kPairSmemBytes)));
+      pair_attr_set = true;
+    }
+    const int pairs = p.total_work < st->sm_count / 2 ? p.total_work : st->sm_count / 2;
+    kernel<<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(map_a, map_b, p);
+    CROQ_CUDA_TRY(cudaGetLastError());
+    return CROQ_OK;
+  }
   rc = encode_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rhs->ptr, N, K, kBlockN,
                             kBlockK);
   if (rc != CROQ_OK) return rc;
