@@ -312,6 +312,264 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap map_a,
   if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
 }
 
+// ------------------------------------------------------------ CTA-pair form --
+// A sparse MMA consumes B at twice the rate of a dense one, so the single-CTA
+// kernel is bound by L2 -> SM operand traffic (80 KB per 512 tensor cycles).
+// Here two CTAs share a 256x256 tile: each loads its own 128 rows of packed A
+// and 128 rows of B (48 KB per stage and CTA, four stages), rank 0 issues
+// tcgen05.mma.sp.cta_group::2 (M=256, N=256), and each CTA repacks the metadata
+// of its own 128 rows into its own TMEM and stores its own 128 output rows.
+constexpr int kPairStages = 4;
+constexpr uint32_t kPairABytes = 128 * 64 * 2;        // 128 rows x 64 packed f16
+constexpr uint32_t kPairBHalfBytes = 128 * 64 * 2;    // 128 rows x 64 f16
+constexpr uint32_t kPairStageBytes = kPairABytes + 2 * kPairBHalfBytes;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+constexpr int kPairGroupM = 8;
+
+__device__ __forceinline__ void decode_pair_tile(const SparseParams& p, int w, int& m0, int& n0) {
+  const int per_group = kPairGroupM * p.tiles_n;   // tiles are 256x256 here
+  const int g = w / per_group;
+  const int first_m = g * kPairGroupM;
+  const int rows = min(kPairGroupM, p.tiles_m - first_m);
+  const int r = w - g * per_group;
+  const int tn = r / rows;
+  const int tm = first_m + (r - tn * rows);
+  m0 = tm * 256;
+  n0 = tn * 256;
+}
+
+__device__ __forceinline__ void umma_sp_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t tmem_e, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::2.kind::f16 [%0], %1, %2, [%5], %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_e)
+      : "memory");
+}
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                        const __grid_constant__ CUtensorMap map_b, const SparseParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPairStages];    // used in rank 0
+  __shared__ __align__(8) uint64_t bar_empty[kPairStages];   // one per CTA (multicast commit)
+  __shared__ __align__(8) uint64_t bar_meta_full;            // used in rank 0: both CTAs' metadata are in TMEM
+  __shared__ __align__(8) uint64_t bar_chunk_done;           // one per CTA (multicast commit)
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_chunks = (p.K + kChunkK - 1) / kChunkK;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_meta_full), 8);   // four repack warps in each CTA
+    mbar_init(smem_u32(&bar_chunk_done), 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      int m0, n0;
+      decode_pair_tile(p, w, m0, n0);
+      const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr);
+        if (!ok) break;
+        const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
+        const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+        const int a_row = m0 + static_cast<int>(rank) * 128, b_row = n0 + static_cast<int>(rank) * 128;
+        if (elect_one()) {
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2u * kPairStageBytes);
+          tma_load_2d_pair(a_dst, &map_a, full_leader, kb * 64, a_row);
+          tma_load_2d_pair(a_dst + kPairABytes, &map_b, full_leader, kb * kBlockK, b_row);
+          tma_load_2d_pair(a_dst + kPairABytes + kPairBHalfBytes, &map_b, full_leader, kb * kBlockK + 64, b_row);
+        }
+        if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 1000000ull) {
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------- MMA issuer (leader CTA) --
+    constexpr uint32_t idesc = umma_idesc(kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16,
+                                          256, 256, /*sparse=*/true);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t meta_phase = 0;
+    bool ok = true;
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      for (int c = 0; c < num_chunks && ok; ++c) {
+        const int k0 = c * kChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
+        ok = mbar_wait(smem_u32(&bar_meta_full), meta_phase, abort_ptr);
+        if (!ok) break;
+        meta_phase ^= 1u;
+        tc_fence_after_sync();
+        for (int kb = 0; kb < kb_in_chunk; ++kb) {
+          ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * kPairStageBytes;
+          const uint64_t adesc = umma_desc_k_sw128(a_src);
+          const uint64_t bdesc0 = umma_desc_k_sw128(a_src + kPairABytes);
+          const uint64_t bdesc1 = umma_desc_k_sw128(a_src + kPairABytes + kPairBHalfBytes);
+          const uint32_t tmem_e = tmem_base + static_cast<uint32_t>(kMetaCol0 + 4 * kb);
+          if (elect_one()) {
+            umma_sp_f16_pair(tmem_base, adesc, bdesc0, tmem_e, idesc, (c | kb) != 0 ? 1u : 0u);
+            umma_sp_f16_pair(tmem_base, adesc + 2u, bdesc0 + 4u, tmem_e, idesc | 1u, 1u);
+            umma_sp_f16_pair(tmem_base, adesc + 4u, bdesc1, tmem_e + 2u, idesc, 1u);
+            umma_sp_f16_pair(tmem_base, adesc + 6u, bdesc1 + 4u, tmem_e + 2u, idesc | 1u, 1u);
+            umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (elect_one()) umma_commit_pair(smem_u32(&bar_chunk_done), 3);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------ metadata repack + epilogue --
+    const int quarter = warp & 3;
+    const int dp = quarter * 32 + lane;
+    const int row_lo_in_tile = (dp >> 4) * 16 + (dp & 7);
+    const int khalf = (dp >> 3) & 1;
+    const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    const size_t meta_pitch = static_cast<size_t>(p.K) / 8;
+    uint32_t done_phase = 0;
+    bool pending = false;
+    bool ok = true;
+    int prev_m0 = 0, prev_n0 = 0;
+    bool have_prev_tile = false;
+
+    auto epilogue = [&](int m0, int n0) {
+      const int row = m0 + static_cast<int>(rank) * 128 + dp;
+      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+      for (int cc = 0; cc < 256 / 32; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + lane_field + cc * 32, v);
+        tmem_ld_wait_on(v);
+        const int col0 = n0 + cc * 32;
+        if (row < p.M && col0 < p.N) {
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+    };
+
+    for (int w = pair; w < p.total_work && ok; w += num_pairs) {
+      int m0, n0;
+      decode_pair_tile(p, w, m0, n0);
+      const int r_lo = m0 + static_cast<int>(rank) * 128 + row_lo_in_tile, r_hi = r_lo + 8;
+      const uint8_t* meta_lo = p.meta + static_cast<size_t>(min(r_lo, p.M - 1)) * meta_pitch;
+      const uint8_t* meta_hi = p.meta + static_cast<size_t>(min(r_hi, p.M - 1)) * meta_pitch;
+      for (int c = 0; c < num_chunks; ++c) {
+        if (pending) {
+          ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
+          if (!ok) break;
+          done_phase ^= 1u;
+          tc_fence_after_sync();
+          pending = false;
+          if (c == 0 && have_prev_tile) epilogue(prev_m0, prev_n0);
+        }
+        const int k0 = c * kChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
+        for (int kb = 0; kb < kb_in_chunk; ++kb) {
+          const size_t off = static_cast<size_t>(k0) / 8 + static_cast<size_t>(kb) * 16;
+          const bool first_ok = off + 8 <= meta_pitch, second_ok = off + 16 <= meta_pitch;
+          const uint2 z = make_uint2(0u, 0u);
+          const uint2 lo0 = (r_lo < p.M && first_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_lo + off)) : z;
+          const uint2 lo1 = (r_lo < p.M && second_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_lo + off + 8)) : z;
+          const uint2 hi0 = (r_hi < p.M && first_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_hi + off)) : z;
+          const uint2 hi1 = (r_hi < p.M && second_ok) ? __ldg(reinterpret_cast<const uint2*>(meta_hi + off + 8)) : z;
+          const uint32_t l[4] = {lo0.x, lo0.y, lo1.x, lo1.y}, h[4] = {hi0.x, hi0.y, hi1.x, hi1.y};
+          uint32_t wd[4];
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t lo16 = khalf ? (l[s] >> 16) : (l[s] & 0xFFFFu);
+            const uint32_t hi16 = khalf ? (h[s] >> 16) : (h[s] & 0xFFFFu);
+            wd[s] = lo16 | (hi16 << 16);
+          }
+          tmem_st_32x32_x4(tmem_base + lane_field + static_cast<uint32_t>(kMetaCol0 + 4 * kb), wd[0],
+                           wd[1], wd[2], wd[3]);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_meta_full), 0));
+        pending = true;
+      }
+      prev_m0 = m0;
+      prev_n0 = n0;
+      have_prev_tile = true;
+    }
+    if (ok && pending) {
+      ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
+      if (ok) {
+        tc_fence_after_sync();
+        if (have_prev_tile) epilogue(prev_m0, prev_n0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_word != 0) *p.status = abort_word;
+}
+
 template <bool kBf16>
 int launch_sparse(const croq_view2* lhs_packed, const croq_view2* lhs_meta, const croq_view2* rhs,
                   const croq_view2* output, cudaStream_t stream) {
@@ -336,6 +594,25 @@ int launch_sparse(const croq_view2* lhs_packed, const croq_view2* lhs_meta, cons
   CUtensorMap map_a, map_b;
   rc = encode_tensor_map_2d(&map_a, dt, 2, lhs_packed->ptr, M, K / 2, kBlockM, 64);
   if (rc != CROQ_OK) return rc;
+  if (M > kBlockM && st->sm_count >= 2) {
+    // CTA pairs on 256x256 tiles
+    p.tiles_m = (M + 255) / 256;
+    p.tiles_n = (N + 255) / 256;
+    p.total_work = p.tiles_m * p.tiles_n;
+    rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, 128, 64);
+    if (rc != CROQ_OK) return rc;
+    auto pair_kernel = gemm_sparse_pair_kernel<kBf16>;
+    static bool pair_attr_set = false;
+    if (!pair_attr_set) {
+      CROQ_CUDA_TRY(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kPairSmemBytes)));
+      pair_attr_set = true;
+    }
+    const int pairs = p.total_work < st->sm_count / 2 ? p.total_work : st->sm_count / 2;
+    pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(map_a, map_b, p);
+    CROQ_CUDA_TRY(cudaGetLastError());
+    return CROQ_OK;
+  }
   rc = encode_tensor_map_2d(&map_b, dt, 2, rhs->ptr, N, K, kBlockN, 64);
   if (rc != CROQ_OK) return rc;
   auto kernel = gemm_sparse_kernel<kBf16>;
