@@ -68,6 +68,28 @@ class FusedExpertParallel:
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self._lib = _lib.load()
 
+    def _route(self, logits):
+        """Routing through the allocation-free entry point when the problem fits its
+        built-in scratch (no allocator traffic inside the step)."""
+        T = logits.shape[0]
+        if ((T + 63) // 64) * self.E > 65536:
+            return api.moe_route_topk(logits, self.k)
+        k, E, dev = self.k, self.E, self.dev
+        out = dict(
+            topk_idx=torch.empty((T, k), dtype=torch.int32, device=dev),
+            topk_w=torch.empty((T, k), dtype=torch.float32, device=dev),
+            expert_counts=torch.empty((E,), dtype=torch.int32, device=dev),
+            expert_offsets=torch.empty((E + 1,), dtype=torch.int32, device=dev),
+            perm_to_src=torch.empty((T * k,), dtype=torch.int32, device=dev),
+            src_to_perm=torch.empty((T * k,), dtype=torch.int32, device=dev),
+        )
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._lib.croq_moe_route_topk_noalloc(
+            _v2(logits), k, 1, _v2(out["topk_idx"]), _v2(out["topk_w"]), _v1(out["expert_counts"]),
+            _v1(out["expert_offsets"]), _v1(out["perm_to_src"]), _v1(out["src_to_perm"]), stream)
+        _lib.check(rc, "croq_moe_route_topk_noalloc")
+        return out
+
     def _barrier(self):
         """Stream-ordered barrier: every rank's earlier kernels are complete
         before any rank's later kernels start."""
@@ -85,7 +107,7 @@ class FusedExpertParallel:
                 timers.append((name, ev))
 
         mark("start")
-        r = api.moe_route_topk(logits, k)
+        r = self._route(logits)
         mark("route")
         # counts of every rank -> placement of my rows in the owners' buffers (all on the device)
         counts = torch.empty((self.world, E), dtype=torch.int32, device=self.dev)
