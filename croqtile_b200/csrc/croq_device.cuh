@@ -487,4 +487,85 @@ __device__ __forceinline__ uint16_t pack1(float v) {
   return static_cast<uint16_t>(pack2<kBf16>(v, 0.0f) & 0xFFFFu);
 }
 
+// -------------------------------------------------- coalesced tile stores --
+
+// An accumulator read from TMEM sits one output ROW per lane, so a direct
+// 16-byte store per lane touches 32 different 128-byte lines per instruction
+// and the load/store unit serialises them: ~4000 cycles for a 128x256 tile.
+// This helper turns a 32-row block (row = lane, kChunks 16-byte pieces per row)
+// through a per-warp staging area in shared memory so that every global store
+// instruction covers 32/kChunks whole row segments of kChunks*16 bytes.
+// The staging layout XOR-swizzles the piece index with the row, which keeps
+// both the row-per-lane writes and the segment-per-8-lanes reads free of bank
+// conflicts. `stage` is this warp's area of 32*kChunks*16 bytes (16-byte
+// aligned); rows >= rows_valid are not stored. All 32 lanes must call.
+template <int kChunks>
+__device__ __forceinline__ void warp_store_rows(uint16_t* out_block, size_t ld, int rows_valid,
+                                                uint4* stage, const uint4 (&pk)[kChunks],
+                                                int lane) {
+  static_assert(kChunks == 8 || kChunks == 4, "row segments of 128 or 64 bytes");
+  constexpr int kRowsPerStore = 32 / kChunks;
+  {
+    const int swz = (kChunks == 8) ? (lane & 7) : ((lane >> 1) & 3);
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) stage[lane * kChunks + (c ^ swz)] = pk[c];
+  }
+  __syncwarp();
+  const int c = lane % kChunks;
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i) {
+    const int r = i * kRowsPerStore + lane / kChunks;
+    const int swz = (kChunks == 8) ? (r & 7) : ((r >> 1) & 3);
+    const uint4 v = stage[r * kChunks + (c ^ swz)];
+    if (r < rows_valid) *reinterpret_cast<uint4*>(out_block + static_cast<size_t>(r) * ld + c * 8) = v;
+  }
+  __syncwarp();
+}
+
+// Drains kCols fp32 accumulator columns of the calling warp's 32 TMEM lanes
+// (taddr = lane-quarter field + first column) into 16-bit output rows
+// row0 .. row0+31, columns n0 .. n0+kCols-1, clipped to m_end / n_end. Whole,
+// 16-byte aligned 64-column blocks go through the staged coalesced store; a
+// ragged or unaligned block falls back to one row per lane. `stage` is the
+// warp's 4 KB staging area. All 32 lanes must call.
+template <bool kBf16, int kCols>
+__device__ __forceinline__ void tmem_store_rows(uint32_t taddr, uint16_t* out, size_t ld, int row0,
+                                                int m_end, int n0, int n_end, bool vec_ok,
+                                                uint4* stage, int lane) {
+  static_assert(kCols % 64 == 0, "whole 64-column blocks");
+#pragma unroll 1
+  for (int cb = 0; cb < kCols / 64; ++cb) {
+    const int col0 = n0 + cb * 64;
+    if (col0 >= n_end) break;   // warp-uniform
+    uint32_t v0[32], v1[32];
+    tmem_ld_32x32(taddr + cb * 64, v0);
+    tmem_ld_32x32(taddr + cb * 64 + 32, v1);
+    tmem_ld_wait_on(v0);
+    tmem_ld_wait_on(v1);
+    if (vec_ok && ((col0 & 7) == 0) && col0 + 64 <= n_end) {
+      uint4 pk[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        pk[q].x = pack2<kBf16>(__uint_as_float(v0[q * 8 + 0]), __uint_as_float(v0[q * 8 + 1]));
+        pk[q].y = pack2<kBf16>(__uint_as_float(v0[q * 8 + 2]), __uint_as_float(v0[q * 8 + 3]));
+        pk[q].z = pack2<kBf16>(__uint_as_float(v0[q * 8 + 4]), __uint_as_float(v0[q * 8 + 5]));
+        pk[q].w = pack2<kBf16>(__uint_as_float(v0[q * 8 + 6]), __uint_as_float(v0[q * 8 + 7]));
+        pk[4 + q].x = pack2<kBf16>(__uint_as_float(v1[q * 8 + 0]), __uint_as_float(v1[q * 8 + 1]));
+        pk[4 + q].y = pack2<kBf16>(__uint_as_float(v1[q * 8 + 2]), __uint_as_float(v1[q * 8 + 3]));
+        pk[4 + q].z = pack2<kBf16>(__uint_as_float(v1[q * 8 + 4]), __uint_as_float(v1[q * 8 + 5]));
+        pk[4 + q].w = pack2<kBf16>(__uint_as_float(v1[q * 8 + 6]), __uint_as_float(v1[q * 8 + 7]));
+      }
+      warp_store_rows<8>(out + static_cast<size_t>(row0) * ld + col0, ld, m_end - row0, stage, pk,
+                         lane);
+    } else if (row0 + lane < m_end) {
+      uint16_t* out_row = out + static_cast<size_t>(row0 + lane) * ld + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (col0 + i < n_end) out_row[i] = pack1<kBf16>(__uint_as_float(v0[i]));
+        if (col0 + 32 + i < n_end) out_row[32 + i] = pack1<kBf16>(__uint_as_float(v1[i]));
+      }
+    }
+  }
+}
+
 }  // namespace croq

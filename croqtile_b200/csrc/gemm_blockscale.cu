@@ -57,7 +57,13 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kABytes = kBlockM * kBlockK;
 constexpr uint32_t kBBytes = kBlockN * kBlockK;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+// Output staging for the coalesced store: each promotion warp owns 32 rows of
+// 128-byte (dense) or 64-byte (grouped: the tile tables need the room) segments.
+__host__ __device__ constexpr int epi_chunks(int mode) { return mode == 0 ? 8 : 4; }
+constexpr size_t smem_bytes(int mode) {
+  return static_cast<size_t>(kStages) * kStageBytes + 1024 +
+         static_cast<size_t>(kEpiWarps) * 32 * epi_chunks(mode) * 16;
+}
 constexpr int kGroupM = 16;  // M tiles per rasterisation group
 
 enum Mode : int { kDense = 0, kGrouped = 1, kGroupedSwiGLU = 2 };
@@ -302,6 +308,10 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
     const int half = (warp - 4) >> 2;
     const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    constexpr int kChunks = epi_chunks(kMode);
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes) +
+        (warp - 4) * 32 * kChunks;
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -362,7 +372,32 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       if constexpr (kMode == kGroupedSwiGLU) {
         // out[row, n0 + half*64 + c] = silu(gate_c) * up_c, c = 0..63
         const int col_base = t.n0 + half * 64;
-        if (row < t.m_end && col_base < (p.N >> 1)) {
+        const int row0 = t.m0 + quarter * 32;
+        if (vec_ok && col_base + 64 <= (p.N >> 1)) {
+          // whole 64-column block: staged, coalesced store
+          uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+#pragma unroll
+          for (int b = 0; b < 8 / kChunks; ++b) {
+            uint4 pk[kChunks];
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+              const int q = b * kChunks + c;
+              float r[8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 g = acc[q * 4 + j], u = acc[32 + q * 4 + j];
+                r[2 * j] = (g.x / (1.0f + expf(-g.x))) * u.x;
+                r[2 * j + 1] = (g.y / (1.0f + expf(-g.y))) * u.y;
+              }
+              pk[c].x = pack2<kBf16>(r[0], r[1]);
+              pk[c].y = pack2<kBf16>(r[2], r[3]);
+              pk[c].z = pack2<kBf16>(r[4], r[5]);
+              pk[c].w = pack2<kBf16>(r[6], r[7]);
+            }
+            warp_store_rows<kChunks>(out_block + b * kChunks * 8, p.out_ld, t.m_end - row0,
+                                     out_stage, pk, lane);
+          }
+        } else if (row < t.m_end && col_base < (p.N >> 1)) {
           uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
@@ -373,40 +408,36 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
               r[2 * j] = (g.x / (1.0f + expf(-g.x))) * u.x;
               r[2 * j + 1] = (g.y / (1.0f + expf(-g.y))) * u.y;
             }
-            if (vec_ok && col_base + q * 8 + 8 <= (p.N >> 1)) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(r[0], r[1]);
-              pk.y = pack2<kBf16>(r[2], r[3]);
-              pk.z = pack2<kBf16>(r[4], r[5]);
-              pk.w = pack2<kBf16>(r[6], r[7]);
-              *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
-            } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col_base + q * 8 + j < (p.N >> 1)) out_row[q * 8 + j] = pack1<kBf16>(r[j]);
-            }
+            for (int j = 0; j < 8; ++j)
+              if (col_base + q * 8 + j < (p.N >> 1)) out_row[q * 8 + j] = pack1<kBf16>(r[j]);
           }
         }
       } else {
         const int col_base = t.n0 + half * 128;
-        if (row < t.m_end && col_base < p.N) {
+        const int row0 = t.m0 + quarter * 32;
+        if (vec_ok && col_base + 128 <= p.N) {
+          uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+#pragma unroll
+          for (int b = 0; b < 16 / kChunks; ++b) {
+            uint4 pk[kChunks];
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+              const int q = b * kChunks + c;
+              pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+              pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+              pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+              pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+            }
+            warp_store_rows<kChunks>(out_block + b * kChunks * 8, p.out_ld, t.m_end - row0,
+                                     out_stage, pk, lane);
+          }
+        } else if (row < t.m_end && col_base < p.N) {
           uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
-          if (vec_ok && col_base + 128 <= p.N) {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-              pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-              pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-              pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
-              *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
-              if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
-            }
+          for (int i = 0; i < 64; ++i) {
+            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
           }
         }
       }
@@ -440,7 +471,8 @@ constexpr int kPairStages = 6;
 constexpr uint32_t kPairABytes = 128 * kBlockK;
 constexpr uint32_t kPairBBytes = 128 * kBlockK;
 constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes;
-constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024 +
+                                  static_cast<size_t>(kEpiWarps) * 32 * 8 * 16;  // + output staging
 constexpr int kPairGroupM = 8;
 
 __device__ __forceinline__ void decode_pair_tile(const BlockScaleParams& p, int w, int& m0, int& n0) {
@@ -573,6 +605,9 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const int half = (warp - 4) >> 2;
     const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) +
+        (warp - 4) * 32 * 8;
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -617,24 +652,28 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         buf ^= 1;
       }
       if (!ok) break;
-      if (row < p.M && col_base < p.N) {
+      const int row0 = m0 + static_cast<int>(rank) * 128 + quarter * 32;
+      if (vec_ok && col_base + 128 <= p.N) {
+        uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          uint4 pk[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int q = b * 8 + c;
+            pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+            pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+            pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+            pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+          }
+          warp_store_rows<8>(out_block + b * 64, p.out_ld, p.M - row0, out_stage, pk, lane);
+        }
+      } else if (row < p.M && col_base < p.N) {
         uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
-        if (vec_ok && col_base + 128 <= p.N) {
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            uint4 pk;
-            pk.x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-            pk.y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-            pk.z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-            pk.w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
-            *reinterpret_cast<uint4*>(out_row + q * 8) = pk;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
-            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
-          }
+        for (int i = 0; i < 64; ++i) {
+          if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+          if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
         }
       }
     }
@@ -668,10 +707,10 @@ int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b, const Bloc
       return record_text_error(CROQ_ERR_UNSUPPORTED,
                                "block-scaled kernel was built with an unexpected register count");
     CROQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kSmemBytes)));
+                                       static_cast<int>(smem_bytes(kMode))));
     attr_set = true;
   }
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  kernel<<<grid, kThreads, smem_bytes(kMode), stream>>>(map_a, map_b, p);
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

@@ -30,7 +30,8 @@ constexpr int kTmemCols = 512;  // two 256-column fp32 accumulators
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
 constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 +
+                              4 * 4096;  // + output staging, 4 KB per epilogue warp
 
 struct DenseParams {
   uint16_t* out;
@@ -202,6 +203,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes) + quarter * 256;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -211,35 +214,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
       ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = t.m0 + quarter * 32 + lane;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
-#pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        const int col0 = t.n0 + c * 32;
-        if (row < t.m_end && col0 < t.n_end) {
-          if (vec_ok && ((col0 & 7) == 0) && col0 + 32 <= t.n_end) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col0 + i < t.n_end) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
-            }
-          }
-        }
-      }
+      tmem_store_rows<kBf16, kBlockN>(taddr, p.out, static_cast<size_t>(p.N), t.m0 + quarter * 32,
+                                      t.m_end, t.n0, t.n_end, vec_ok, out_stage, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
@@ -271,7 +249,8 @@ constexpr int kPairStages = 6;
 constexpr uint32_t kPairABytes = 128 * kBlockK * 2;
 constexpr uint32_t kPairBBytes = 128 * kBlockK * 2;
 constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes;
-constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024 +
+                                  4 * 4096;  // + output staging
 
 template <bool kBf16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -393,6 +372,8 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) + quarter * 256;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -402,34 +383,11 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       ok = mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, abort_ptr);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = t.m0 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(acc * kPairN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
-#pragma unroll 1
-      for (int c = 0; c < kPairN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait_on(v);
-        const int col0 = t.n0 + c * 32;
-        if (row < t.m_end && col0 < t.n_end) {
-          if (vec_ok && ((col0 & 7) == 0) && col0 + 32 <= t.n_end) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < t.n_end) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
-          }
-        }
-      }
+      tmem_store_rows<kBf16, kPairN>(taddr, p.out, static_cast<size_t>(p.N),
+                                     t.m0 + static_cast<int>(rank) * 128 + quarter * 32, t.m_end,
+                                     t.n0, t.n_end, vec_ok, out_stage, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[acc]), 0));

@@ -41,7 +41,8 @@ constexpr int kChunkK = 8192;       // K positions whose metadata fit 256 column
 constexpr uint32_t kABytes = kBlockM * 64 * 2;       // 128 rows x 64 packed f16
 constexpr uint32_t kBHalfBytes = kBlockN * 64 * 2;   // 256 rows x 64 f16
 constexpr uint32_t kStageBytes = kABytes + 2 * kBHalfBytes;
-constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 +
+                              4 * 4096;  // + output staging, 4 KB per epilogue warp
 constexpr int kGroupM = 16;
 
 struct SparseParams {
@@ -213,33 +214,11 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap map_a,
     int prev_m0 = 0, prev_n0 = 0;
     bool have_prev_tile = false;
 
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes) + quarter * 256;
     auto epilogue = [&](int m0, int n0) {
-      const int row = m0 + dp;
-      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
-#pragma unroll 1
-      for (int cc = 0; cc < kBlockN / 32; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_field + cc * 32, v);
-        tmem_ld_wait_on(v);
-        const int col0 = n0 + cc * 32;
-        if (row < p.M && col0 < p.N) {
-          if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
-          }
-        }
-      }
+      tmem_store_rows<kBf16, kBlockN>(tmem_base + lane_field, p.out, static_cast<size_t>(p.N),
+                                      m0 + quarter * 32, p.M, n0, p.N, vec_ok, out_stage, lane);
       tc_fence_before_sync();
     };
 
@@ -323,7 +302,8 @@ constexpr int kPairStages = 4;
 constexpr uint32_t kPairABytes = 128 * 64 * 2;        // 128 rows x 64 packed f16
 constexpr uint32_t kPairBHalfBytes = 128 * 64 * 2;    // 128 rows x 64 f16
 constexpr uint32_t kPairStageBytes = kPairABytes + 2 * kPairBHalfBytes;
-constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024 +
+                                  4 * 4096;  // + output staging
 constexpr int kPairGroupM = 8;
 
 __device__ __forceinline__ void decode_pair_tile(const SparseParams& p, int w, int& m0, int& n0) {
@@ -476,33 +456,12 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     int prev_m0 = 0, prev_n0 = 0;
     bool have_prev_tile = false;
 
+    uint4* const out_stage = reinterpret_cast<uint4*>(
+        smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) + quarter * 256;
     auto epilogue = [&](int m0, int n0) {
-      const int row = m0 + static_cast<int>(rank) * 128 + dp;
-      uint16_t* out_row = p.out + static_cast<size_t>(row) * p.N;
-#pragma unroll 1
-      for (int cc = 0; cc < 256 / 32; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_field + cc * 32, v);
-        tmem_ld_wait_on(v);
-        const int col0 = n0 + cc * 32;
-        if (row < p.M && col0 < p.N) {
-          if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              pk.y = pack2<kBf16>(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              pk.z = pack2<kBf16>(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              pk.w = pack2<kBf16>(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(out_row + col0 + q * 8) = pk;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) out_row[col0 + i] = pack1<kBf16>(__uint_as_float(v[i]));
-          }
-        }
-      }
+      tmem_store_rows<kBf16, 256>(tmem_base + lane_field, p.out, static_cast<size_t>(p.N),
+                                  m0 + static_cast<int>(rank) * 128 + quarter * 32, p.M, n0, p.N,
+                                  vec_ok, out_stage, lane);
       tc_fence_before_sync();
     };
 
