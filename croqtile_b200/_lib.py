@@ -35,6 +35,13 @@ STATUS = {
 }
 CROQ_DTYPE_F16 = 0
 CROQ_DTYPE_BF16 = 1
+CROQ_DTYPE_F32 = 2
+
+
+class Epilogue(Structure):
+    """Layout of ``croq_epilogue``."""
+    _fields_ = [("out_dtype", c_int), ("transposed", c_int), ("bias", ctypes.c_float)]
+
 
 P1, P2, P3 = POINTER(View1), POINTER(View2), POINTER(View3)
 
@@ -47,8 +54,12 @@ SIGNATURES = {
     "croq_last_kernel_clock": (c_int, [POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "croq_matmul_f16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
     "croq_matmul_bf16": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_void_p]),
+    "croq_matmul_ex": (c_int, [P2, P2, P2, P1, P1, c_int, c_int, c_int, POINTER(Epilogue), c_void_p]),
     "croq_blockscale_gemm_e4m3": (c_int, [P2, P2, P2, P2, P2, c_int, c_void_p]),
+    "croq_blockscale_gemm_e4m3_ex": (c_int, [P2, P2, P2, P2, P2, c_int, c_int, c_void_p]),
     "croq_gemm_sp_f16": (c_int, [P2, P2, P2, P2, c_int, c_void_p]),
+    "croq_sparse24_encode_f16": (c_int, [P2, P2, P2, c_void_p]),
+    "croq_sparse24_prepack_meta": (c_int, [P2, P2, c_int, c_void_p]),
     "croq_moe_route_topk": (c_int, [P2, c_int, c_int, P2, P2, P1, P1, P1, P1, c_void_p]),
     "croq_moe_route_topk_noalloc": (c_int, [P2, c_int, c_int, P2, P2, P1, P1, P1, P1, c_void_p]),
     "croq_moe_permute": (c_int, [P2, P1, c_int, P2, c_void_p]),

@@ -15,7 +15,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import CROQ_DTYPE_BF16, CROQ_DTYPE_F16, View1, View2, View3
+from ._lib import CROQ_DTYPE_BF16, CROQ_DTYPE_F16, CROQ_DTYPE_F32, Epilogue, View1, View2, View3
 
 
 def _stream() -> ctypes.c_void_p:
@@ -93,11 +93,45 @@ def matmul(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor | None = N
     return output
 
 
+_DTYPE_FLAG = {torch.float16: CROQ_DTYPE_F16, torch.bfloat16: CROQ_DTYPE_BF16,
+               torch.float32: CROQ_DTYPE_F32}
+
+
+def matmul_ex(lhs: torch.Tensor, rhs: torch.Tensor, output: torch.Tensor | None = None,
+              schedule_m: torch.Tensor | None = None, schedule_n: torch.Tensor | None = None,
+              sched_tile_m: int = 256, sched_tile_n: int = 256, *,
+              out_dtype: torch.dtype | None = None, transposed: bool = False,
+              bias: float = 0.0) -> torch.Tensor:
+    """``matmul`` with the reference's store variants (``croq_matmul_ex``): f16 / bf16 / f32
+    output, transposed store (output [N,M]), scalar bias added before rounding."""
+    lib = _lib.load()
+    M, N = lhs.shape[0], rhs.shape[0]
+    if output is None:
+        output = torch.empty((N, M) if transposed else (M, N),
+                             dtype=out_dtype or lhs.dtype, device=lhs.device)
+    _need_cuda(lhs, rhs, output, schedule_m, schedule_n)
+    if lhs.dtype != rhs.dtype or lhs.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("lhs and rhs must share float16 or bfloat16")
+    if output.dtype not in _DTYPE_FLAG:
+        raise ValueError(f"output dtype must be float16, bfloat16 or float32, got {output.dtype}")
+    for s in (schedule_m, schedule_n):
+        if s is not None and s.dtype != torch.int32:
+            raise ValueError("schedules are s32 arrays")
+    epi = Epilogue(_DTYPE_FLAG[output.dtype], 1 if transposed else 0, float(bias))
+    rc = lib.croq_matmul_ex(_v2(lhs), _v2(rhs), _v2(output), _v1(schedule_m), _v1(schedule_n),
+                            int(sched_tile_m), int(sched_tile_n), _DTYPE_FLAG[lhs.dtype],
+                            ctypes.byref(epi), _stream())
+    _lib.check(rc, "croq_matmul_ex")
+    return output
+
+
 def blockscale_gemm_e4m3(lhs: torch.Tensor, scale_lhs: torch.Tensor, rhs: torch.Tensor,
                          scale_rhs: torch.Tensor, output: torch.Tensor | None = None,
-                         out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                         out_dtype: torch.dtype = torch.bfloat16,
+                         scale_lhs_k_major: bool = False) -> torch.Tensor:
     """FP8 e4m3 GEMM with fp32 scales per 1x128 (lhs) and 128x128 (rhs) block;
-    argument order of the reference's ``blockscale_gemm_e4m3_ws_persis``."""
+    argument order of the reference's ``blockscale_gemm_e4m3_ws_persis``. With
+    ``scale_lhs_k_major`` the lhs scales are stored [K/128, M] instead of [M, K/128]."""
     lib = _lib.load()
     if output is None:
         output = torch.empty((lhs.shape[0], rhs.shape[0]), dtype=out_dtype, device=lhs.device)
@@ -106,8 +140,12 @@ def blockscale_gemm_e4m3(lhs: torch.Tensor, scale_lhs: torch.Tensor, rhs: torch.
         raise ValueError("lhs and rhs must be float8_e4m3fn")
     if scale_lhs.dtype != torch.float32 or scale_rhs.dtype != torch.float32:
         raise ValueError("scales are f32")
-    rc = lib.croq_blockscale_gemm_e4m3(_v2(lhs), _v2(scale_lhs), _v2(rhs), _v2(scale_rhs),
-                                       _v2(output), _out_dtype_flag(output), _stream())
+    if scale_lhs_k_major:
+        rc = lib.croq_blockscale_gemm_e4m3_ex(_v2(lhs), _v2(scale_lhs), _v2(rhs), _v2(scale_rhs),
+                                              _v2(output), _out_dtype_flag(output), 1, _stream())
+    else:
+        rc = lib.croq_blockscale_gemm_e4m3(_v2(lhs), _v2(scale_lhs), _v2(rhs), _v2(scale_rhs),
+                                           _v2(output), _out_dtype_flag(output), _stream())
     _lib.check(rc, "croq_blockscale_gemm_e4m3")
     return output
 
@@ -126,6 +164,37 @@ def gemm_sp_f16(lhs_packed: torch.Tensor, lhs_meta: torch.Tensor, rhs: torch.Ten
                               _out_dtype_flag(output), _stream())
     _lib.check(rc, "croq_gemm_sp_f16")
     return output
+
+
+def sparse24_encode(dense: torch.Tensor):
+    """2:4 compressor: dense f16/bf16 [M,K] -> (packed [M,K/2], meta u8 [M,K/8]) in the
+    reference's host encoding (``croq_sparse24_encode_f16``)."""
+    lib = _lib.load()
+    _need_cuda(dense)
+    if dense.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("sparse24_encode takes 16-bit values")
+    M, K = dense.shape
+    if K % 8:
+        raise ValueError("K must be a multiple of 8")
+    packed = torch.empty((M, K // 2), dtype=dense.dtype, device=dense.device)
+    meta = torch.empty((M, K // 8), dtype=torch.uint8, device=dense.device)
+    rc = lib.croq_sparse24_encode_f16(_v2(dense), _v2(packed), _v2(meta), _stream())
+    _lib.check(rc, "croq_sparse24_encode_f16")
+    return packed, meta
+
+
+def sparse24_prepack_meta(meta: torch.Tensor, layout: int = 1) -> torch.Tensor:
+    """u8 [M,K/8] metadata -> u32 [M,K/32] words in the reference's ``prepack`` (layout 1)
+    or ``prepack_v2`` (layout 2) order; returned as int32 storage."""
+    lib = _lib.load()
+    _need_cuda(meta)
+    if meta.dtype != torch.uint8:
+        raise ValueError("metadata is u8")
+    M, KM = meta.shape
+    out = torch.empty((M, KM // 4), dtype=torch.int32, device=meta.device)
+    rc = lib.croq_sparse24_prepack_meta(_v2(meta), _v2(out), int(layout), _stream())
+    _lib.check(rc, "croq_sparse24_prepack_meta")
+    return out
 
 
 # ------------------------------------------------------------------ MoE path --

@@ -500,7 +500,7 @@ __device__ __forceinline__ uint16_t pack1(float v) {
 // conflicts. `stage` is this warp's area of 32*kChunks*16 bytes (16-byte
 // aligned); rows >= rows_valid are not stored. All 32 lanes must call.
 template <int kChunks>
-__device__ __forceinline__ void warp_store_rows(uint16_t* out_block, size_t ld, int rows_valid,
+__device__ __forceinline__ void warp_store_rows(void* out_block, size_t ld_bytes, int rows_valid,
                                                 uint4* stage, const uint4 (&pk)[kChunks],
                                                 int lane) {
   static_assert(kChunks == 8 || kChunks == 4, "row segments of 128 or 64 bytes");
@@ -512,12 +512,13 @@ __device__ __forceinline__ void warp_store_rows(uint16_t* out_block, size_t ld, 
   }
   __syncwarp();
   const int c = lane % kChunks;
+  uint8_t* const out_bytes = static_cast<uint8_t*>(out_block) + c * 16;
 #pragma unroll
   for (int i = 0; i < kChunks; ++i) {
     const int r = i * kRowsPerStore + lane / kChunks;
     const int swz = (kChunks == 8) ? (r & 7) : ((r >> 1) & 3);
     const uint4 v = stage[r * kChunks + (c ^ swz)];
-    if (r < rows_valid) *reinterpret_cast<uint4*>(out_block + static_cast<size_t>(r) * ld + c * 8) = v;
+    if (r < rows_valid) *reinterpret_cast<uint4*>(out_bytes + static_cast<size_t>(r) * ld_bytes) = v;
   }
   __syncwarp();
 }
@@ -555,8 +556,8 @@ __device__ __forceinline__ void tmem_store_rows(uint32_t taddr, uint16_t* out, s
         pk[4 + q].z = pack2<kBf16>(__uint_as_float(v1[q * 8 + 4]), __uint_as_float(v1[q * 8 + 5]));
         pk[4 + q].w = pack2<kBf16>(__uint_as_float(v1[q * 8 + 6]), __uint_as_float(v1[q * 8 + 7]));
       }
-      warp_store_rows<8>(out + static_cast<size_t>(row0) * ld + col0, ld, m_end - row0, stage, pk,
-                         lane);
+      warp_store_rows<8>(out + static_cast<size_t>(row0) * ld + col0, ld * 2, m_end - row0, stage,
+                         pk, lane);
     } else if (row0 + lane < m_end) {
       uint16_t* out_row = out + static_cast<size_t>(row0 + lane) * ld + col0;
 #pragma unroll
@@ -564,6 +565,76 @@ __device__ __forceinline__ void tmem_store_rows(uint32_t taddr, uint16_t* out, s
         if (col0 + i < n_end) out_row[i] = pack1<kBf16>(__uint_as_float(v0[i]));
         if (col0 + 32 + i < n_end) out_row[32 + i] = pack1<kBf16>(__uint_as_float(v1[i]));
       }
+    }
+  }
+}
+
+// Output kinds of the epilogue variants (values of CROQ_DTYPE_*).
+constexpr int kOutF16 = 0, kOutBf16 = 1, kOutF32 = 2;
+
+__device__ __forceinline__ void store_scalar(void* out, size_t index, int out_kind, float v) {
+  if (out_kind == kOutF32) static_cast<float*>(out)[index] = v;
+  else if (out_kind == kOutBf16) static_cast<uint16_t*>(out)[index] = pack1<true>(v);
+  else static_cast<uint16_t*>(out)[index] = pack1<false>(v);
+}
+
+// Epilogue variants of the dense GEMM: `bias` is added to every accumulator
+// before rounding (the reference's `mc += bias`), the result goes out as f16,
+// bf16 or f32, row-major [M, ld] or transposed [N, ld] (mma.store.transp:
+// element (m, n) lands at out[n * ld + m]). Row-major blocks use the staged
+// coalesced store; a transposed block is coalesced as it is (the 32 lanes of
+// a warp hold 32 consecutive m). Same clipping rules as tmem_store_rows.
+template <int kCols>
+__device__ __forceinline__ void tmem_store_rows_ex(uint32_t taddr, void* out, int out_kind,
+                                                   bool transposed, float bias, size_t ld,
+                                                   int row0, int m_end, int n0, int n_end,
+                                                   bool vec_ok, uint4* stage, int lane) {
+  static_assert(kCols % 32 == 0, "whole 32-column blocks");
+  const int elem = (out_kind == kOutF32) ? 4 : 2;
+#pragma unroll 1
+  for (int cb = 0; cb < kCols / 32; ++cb) {
+    const int col0 = n0 + cb * 32;
+    if (col0 >= n_end) break;   // warp-uniform
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + cb * 32, v);
+    tmem_ld_wait_on(v);
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) + bias;
+    const int row = row0 + lane;
+    if (transposed) {
+      if (row < m_end) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < n_end) store_scalar(out, static_cast<size_t>(col0 + i) * ld + row, out_kind, f[i]);
+      }
+    } else if (vec_ok && ((col0 * elem) & 15) == 0 && col0 + 32 <= n_end) {
+      uint8_t* out_block = static_cast<uint8_t*>(out) + (static_cast<size_t>(row0) * ld + col0) * elem;
+      if (out_kind == kOutF32) {
+        uint4 pk[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          pk[q] = make_uint4(__float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]),
+                             __float_as_uint(f[4 * q + 2]), __float_as_uint(f[4 * q + 3]));
+        warp_store_rows<8>(out_block, ld * 4, m_end - row0, stage, pk, lane);
+      } else {
+        uint4 pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (out_kind == kOutBf16) {
+            pk[q] = make_uint4(pack2<true>(f[8 * q], f[8 * q + 1]), pack2<true>(f[8 * q + 2], f[8 * q + 3]),
+                               pack2<true>(f[8 * q + 4], f[8 * q + 5]), pack2<true>(f[8 * q + 6], f[8 * q + 7]));
+          } else {
+            pk[q] = make_uint4(pack2<false>(f[8 * q], f[8 * q + 1]), pack2<false>(f[8 * q + 2], f[8 * q + 3]),
+                               pack2<false>(f[8 * q + 4], f[8 * q + 5]), pack2<false>(f[8 * q + 6], f[8 * q + 7]));
+          }
+        }
+        warp_store_rows<4>(out_block, ld * 2, m_end - row0, stage, pk, lane);
+      }
+    } else if (row < m_end) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_end) store_scalar(out, static_cast<size_t>(row) * ld + col0 + i, out_kind, f[i]);
     }
   }
 }

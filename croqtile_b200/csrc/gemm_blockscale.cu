@@ -71,7 +71,8 @@ constexpr int kMaxExperts = 1024;
 
 struct BlockScaleParams {
   uint16_t* out;
-  const float* scale_a;  // [M, KB]
+  const float* scale_a;  // [M, KB] (sa_row = KB, sa_kb = 1) or K-major [KB, M] (1, M)
+  size_t sa_row, sa_kb;  // element strides of scale_a along rows and K blocks
   const float* scale_b;  // dense [NB, KB]; grouped [E, NB, KB]
   int M, N, K;           // M = rows of lhs (all experts); N = rows of one weight
   int KB, NB;            // number of 128-wide K blocks / N blocks (per expert)
@@ -321,7 +322,7 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       if constexpr (kMode == kDense) t = decode_dense(p, w);
       else t = decode_grouped(p, tile_prefix, offsets_s, w, kTileCols);
       const int row = t.m0 + quarter * 32 + lane;
-      const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.KB;
+      const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.sa_row;
       // Weight-scale rows of this thread's two 64-column loads. Dense/grouped:
       // both lie in the 128-block of columns n0 + half*128. SwiGLU: the first
       // load holds gate columns n0 + half*64.., the second the matching up columns.
@@ -346,7 +347,7 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
         const unsigned long long s0 = pack_f32x2(scale0, scale0);
         const unsigned long long s1 = pack_f32x2(scale1, scale1);
         const int kn = min(kb + 1, num_kb - 1);
-        sa_next = __ldg(sa_ptr + kn);
+        sa_next = __ldg(sa_ptr + static_cast<size_t>(kn) * p.sa_kb);
         sb0_next = __ldg(sb0_ptr + kn);
         if constexpr (kMode == kGroupedSwiGLU) sb1_next = __ldg(sb1_ptr + kn);
         ok = mbar_wait(smem_u32(&bar_mma_done[stage]), phase, abort_ptr);
@@ -394,8 +395,8 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
               pk[c].z = pack2<kBf16>(r[4], r[5]);
               pk[c].w = pack2<kBf16>(r[6], r[7]);
             }
-            warp_store_rows<kChunks>(out_block + b * kChunks * 8, p.out_ld, t.m_end - row0,
-                                     out_stage, pk, lane);
+            warp_store_rows<kChunks>(out_block + b * kChunks * 8, static_cast<size_t>(p.out_ld) * 2,
+                                     t.m_end - row0, out_stage, pk, lane);
           }
         } else if (row < t.m_end && col_base < (p.N >> 1)) {
           uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
@@ -429,8 +430,8 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
               pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
               pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
             }
-            warp_store_rows<kChunks>(out_block + b * kChunks * 8, p.out_ld, t.m_end - row0,
-                                     out_stage, pk, lane);
+            warp_store_rows<kChunks>(out_block + b * kChunks * 8, static_cast<size_t>(p.out_ld) * 2,
+                                     t.m_end - row0, out_stage, pk, lane);
           }
         } else if (row < t.m_end && col_base < p.N) {
           uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
@@ -617,7 +618,7 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       decode_pair_tile(p, w, m0, n0);
       const int row = m0 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const int col_base = n0 + half * 128;
-      const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.KB;
+      const float* sa_ptr = p.scale_a + static_cast<size_t>(min(row, p.M - 1)) * p.sa_row;
       const float* sb_ptr = p.scale_b + static_cast<size_t>(min(col_base >> 7, p.NB - 1)) * p.KB;
       float2 acc[64];
 #pragma unroll
@@ -644,7 +645,7 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         // next block's scales: requested after the arrive, so no global load
         // is in flight when the arrive's release is performed
         const int kn = min(kb + 1, num_kb - 1);
-        sa_next = __ldg(sa_ptr + kn);
+        sa_next = __ldg(sa_ptr + static_cast<size_t>(kn) * p.sa_kb);
         sb_next = __ldg(sb_ptr + kn);
 #pragma unroll
         for (int i = 0; i < 32; ++i) ffma2_packed(acc[32 + i], v[i], s2);
@@ -666,7 +667,8 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
             pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
           }
-          warp_store_rows<8>(out_block + b * 64, p.out_ld, p.M - row0, out_stage, pk, lane);
+          warp_store_rows<8>(out_block + b * 64, static_cast<size_t>(p.out_ld) * 2, p.M - row0,
+                             out_stage, pk, lane);
         }
       } else if (row < p.M && col_base < p.N) {
         uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
@@ -717,7 +719,7 @@ int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b, const Bloc
 
 template <bool kBf16>
 int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const croq_view2* rhs,
-                      const croq_view2* scale_rhs, const croq_view2* output,
+                      const croq_view2* scale_rhs, const croq_view2* output, bool scale_k_major,
                       cudaStream_t stream) {
   int rc = CROQ_OK;
   DeviceState* st = device_state(&rc);
@@ -732,6 +734,8 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
   BlockScaleParams p = {};
   p.out = static_cast<uint16_t*>(output->ptr);
   p.scale_a = static_cast<const float*>(scale_lhs->ptr);
+  p.sa_row = scale_k_major ? 1 : (static_cast<size_t>(K) + kBlockK - 1) / kBlockK;
+  p.sa_kb = scale_k_major ? static_cast<size_t>(M) : 1;
   p.scale_b = static_cast<const float*>(scale_rhs->ptr);
   p.M = M; p.N = N; p.K = K;
   p.KB = (K + kBlockK - 1) / kBlockK;
@@ -791,22 +795,27 @@ int launch_blockscale(const croq_view2* lhs, const croq_view2* scale_lhs, const 
 
 }  // namespace croq
 
-extern "C" int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2* scale_lhs,
-                                         const croq_view2* rhs, const croq_view2* scale_rhs,
-                                         const croq_view2* output, int out_dtype,
-                                         croq_stream stream) {
-  using namespace croq;
+namespace croq {
+namespace {
+
+int blockscale_entry(const croq_view2* lhs, const croq_view2* scale_lhs, const croq_view2* rhs,
+                     const croq_view2* scale_rhs, const croq_view2* output, int out_dtype,
+                     int scale_lhs_layout, croq_stream stream) {
   clear_error();
   if (!view_ok(lhs) || !view_ok(scale_lhs) || !view_ok(rhs) || !view_ok(scale_rhs) ||
       !view_ok(output))
     return CROQ_ERR_NULL;
+  if (scale_lhs_layout != CROQ_SCALE_ROW_MAJOR && scale_lhs_layout != CROQ_SCALE_K_MAJOR)
+    return CROQ_ERR_UNSUPPORTED;
+  const bool k_major = scale_lhs_layout == CROQ_SCALE_K_MAJOR;
   const size_t M = lhs->dims[0], K = lhs->dims[1], N = rhs->dims[0];
   if (rhs->dims[1] != K || output->dims[0] != M || output->dims[1] != N) return CROQ_ERR_SHAPE;
   if (M == 0 || N == 0) return CROQ_ERR_SHAPE;
   if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
   const size_t KB = (K + 127) / 128, NB = (N + 127) / 128;
   if (K != 0) {
-    if (scale_lhs->dims[0] != M || scale_lhs->dims[1] != KB) return CROQ_ERR_SHAPE;
+    if (scale_lhs->dims[0] != (k_major ? KB : M) || scale_lhs->dims[1] != (k_major ? M : KB))
+      return CROQ_ERR_SHAPE;
     if (scale_rhs->dims[0] != NB || scale_rhs->dims[1] != KB) return CROQ_ERR_SHAPE;
   }
   if (out_dtype != CROQ_DTYPE_F16 && out_dtype != CROQ_DTYPE_BF16) return CROQ_ERR_UNSUPPORTED;
@@ -818,8 +827,27 @@ extern "C" int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2
     return CROQ_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return out_dtype == CROQ_DTYPE_BF16
-             ? launch_blockscale<true>(lhs, scale_lhs, rhs, scale_rhs, output, s)
-             : launch_blockscale<false>(lhs, scale_lhs, rhs, scale_rhs, output, s);
+             ? launch_blockscale<true>(lhs, scale_lhs, rhs, scale_rhs, output, k_major, s)
+             : launch_blockscale<false>(lhs, scale_lhs, rhs, scale_rhs, output, k_major, s);
+}
+
+}  // namespace
+}  // namespace croq
+
+extern "C" int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2* scale_lhs,
+                                         const croq_view2* rhs, const croq_view2* scale_rhs,
+                                         const croq_view2* output, int out_dtype,
+                                         croq_stream stream) {
+  return croq::blockscale_entry(lhs, scale_lhs, rhs, scale_rhs, output, out_dtype,
+                                CROQ_SCALE_ROW_MAJOR, stream);
+}
+
+extern "C" int croq_blockscale_gemm_e4m3_ex(const croq_view2* lhs, const croq_view2* scale_lhs,
+                                            const croq_view2* rhs, const croq_view2* scale_rhs,
+                                            const croq_view2* output, int out_dtype,
+                                            int scale_lhs_layout, croq_stream stream) {
+  return croq::blockscale_entry(lhs, scale_lhs, rhs, scale_rhs, output, out_dtype,
+                                scale_lhs_layout, stream);
 }
 
 extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
@@ -860,6 +888,8 @@ extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2*
   BlockScaleParams p = {};
   p.out = static_cast<uint16_t*>(out->ptr);
   p.scale_a = static_cast<const float*>(x_scale->ptr);
+  p.sa_row = x_scale->dims[1];
+  p.sa_kb = 1;
   p.scale_b = static_cast<const float*>(w_scale->ptr);
   p.M = static_cast<int>(R);
   p.N = static_cast<int>(N);

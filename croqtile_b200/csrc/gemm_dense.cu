@@ -35,6 +35,12 @@ constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 
 
 struct DenseParams {
   uint16_t* out;
+  // Epilogue variants (epi_plain == 0): out_ex of out_kind (CROQ_DTYPE_*),
+  // row pitch ld_out elements, optionally transposed, bias added before rounding.
+  void* out_ex;
+  size_t ld_out;
+  int epi_plain, out_kind, transposed;
+  float bias;
   int M, N, K;
   const int* sched_m;
   const int* sched_n;
@@ -203,6 +209,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const bool vec_ok_ex =
+        (((p.ld_out * (p.out_kind == kOutF32 ? 4 : 2)) & 15) == 0) &&
+        ((reinterpret_cast<uintptr_t>(p.out_ex) & 15u) == 0);
     uint4* const out_stage = reinterpret_cast<uint4*>(
         smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes) + quarter * 256;
     int acc = 0;
@@ -216,8 +225,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after_sync();
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      tmem_store_rows<kBf16, kBlockN>(taddr, p.out, static_cast<size_t>(p.N), t.m0 + quarter * 32,
-                                      t.m_end, t.n0, t.n_end, vec_ok, out_stage, lane);
+      if (p.epi_plain) {
+        tmem_store_rows<kBf16, kBlockN>(taddr, p.out, static_cast<size_t>(p.N), t.m0 + quarter * 32,
+                                        t.m_end, t.n0, t.n_end, vec_ok, out_stage, lane);
+      } else {
+        tmem_store_rows_ex<kBlockN>(taddr, p.out_ex, p.out_kind, p.transposed != 0, p.bias, p.ld_out,
+                                    t.m0 + quarter * 32, t.m_end, t.n0, t.n_end, vec_ok_ex,
+                                    out_stage, lane);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
@@ -372,6 +387,9 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------------ epilogue --
     const int quarter = warp & 3;
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+    const bool vec_ok_ex =
+        (((p.ld_out * (p.out_kind == kOutF32 ? 4 : 2)) & 15) == 0) &&
+        ((reinterpret_cast<uintptr_t>(p.out_ex) & 15u) == 0);
     uint4* const out_stage = reinterpret_cast<uint4*>(
         smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) + quarter * 256;
     int acc = 0;
@@ -385,9 +403,14 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after_sync();
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(acc * kPairN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      tmem_store_rows<kBf16, kPairN>(taddr, p.out, static_cast<size_t>(p.N),
-                                     t.m0 + static_cast<int>(rank) * 128 + quarter * 32, t.m_end,
-                                     t.n0, t.n_end, vec_ok, out_stage, lane);
+      const int row0 = t.m0 + static_cast<int>(rank) * 128 + quarter * 32;
+      if (p.epi_plain) {
+        tmem_store_rows<kBf16, kPairN>(taddr, p.out, static_cast<size_t>(p.N), row0, t.m_end, t.n0,
+                                       t.n_end, vec_ok, out_stage, lane);
+      } else {
+        tmem_store_rows_ex<kPairN>(taddr, p.out_ex, p.out_kind, p.transposed != 0, p.bias, p.ld_out,
+                                   row0, t.m_end, t.n0, t.n_end, vec_ok_ex, out_stage, lane);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[acc]), 0));
@@ -410,13 +433,15 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
 int check_dense_views(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
                       const croq_view1* schedule_m, const croq_view1* schedule_n,
-                      int sched_tile_m, int sched_tile_n) {
+                      int sched_tile_m, int sched_tile_n, bool transposed, int out_elem) {
   if (!view_ok(lhs) || !view_ok(rhs) || !view_ok(output)) return CROQ_ERR_NULL;
   const bool has_m = schedule_m != nullptr, has_n = schedule_n != nullptr;
   if (has_m != has_n) return CROQ_ERR_NULL;
   if (has_m && (!view_ok(schedule_m) || !view_ok(schedule_n))) return CROQ_ERR_NULL;
   const size_t M = lhs->dims[0], K = lhs->dims[1], N = rhs->dims[0];
-  if (rhs->dims[1] != K || output->dims[0] != M || output->dims[1] != N) return CROQ_ERR_SHAPE;
+  if (rhs->dims[1] != K) return CROQ_ERR_SHAPE;
+  if (output->dims[0] != (transposed ? N : M) || output->dims[1] != (transposed ? M : N))
+    return CROQ_ERR_SHAPE;
   if (M == 0 || N == 0) return CROQ_ERR_SHAPE;
   if (M > 0x7FFFFFFFull || N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
   if (sched_tile_m <= 0 || sched_tile_n <= 0) return CROQ_ERR_SHAPE;
@@ -427,16 +452,31 @@ int check_dense_views(const croq_view2* lhs, const croq_view2* rhs, const croq_v
   }
   if (!aligned16(lhs->ptr) || !aligned16(rhs->ptr)) return CROQ_ERR_ALIGN;
   if (K != 0 && (K * 2) % 16 != 0) return CROQ_ERR_ALIGN;  // TMA row pitch
-  if ((reinterpret_cast<uintptr_t>(output->ptr) & 1u) != 0) return CROQ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(output->ptr) & static_cast<uintptr_t>(out_elem - 1)) != 0)
+    return CROQ_ERR_ALIGN;
   return CROQ_OK;
+}
+
+// K == 0 with an epilogue: every output element is RN(0 + bias).
+__global__ void fill_bias_kernel(void* out, size_t count, int out_kind, float bias) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+    store_scalar(out, i, out_kind, 0.0f + bias);
 }
 
 template <bool kBf16>
 int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
                  const croq_view1* schedule_m, const croq_view1* schedule_n, int sched_tile_m,
-                 int sched_tile_n, croq_stream stream_) {
+                 int sched_tile_n, const croq_epilogue* epi, croq_stream stream_) {
   clear_error();
-  int rc = check_dense_views(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m, sched_tile_n);
+  const int in_kind = kBf16 ? kOutBf16 : kOutF16;
+  const int out_kind = epi ? epi->out_dtype : in_kind;
+  const bool transposed = epi && epi->transposed != 0;
+  const float bias = epi ? epi->bias : 0.0f;
+  if (out_kind != kOutF16 && out_kind != kOutBf16 && out_kind != kOutF32) return CROQ_ERR_UNSUPPORTED;
+  const int out_elem = out_kind == kOutF32 ? 4 : 2;
+  int rc = check_dense_views(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m, sched_tile_n,
+                             transposed, out_elem);
   if (rc != CROQ_OK) return rc;
   DeviceState* st = device_state(&rc);
   if (st == nullptr) return rc;
@@ -444,12 +484,25 @@ int launch_dense(const croq_view2* lhs, const croq_view2* rhs, const croq_view2*
   const int M = static_cast<int>(lhs->dims[0]);
   const int K = static_cast<int>(lhs->dims[1]);
   const int N = static_cast<int>(rhs->dims[0]);
+  const bool plain = out_kind == in_kind && !transposed && bias == 0.0f;
   if (K == 0) {
-    CROQ_CUDA_TRY(cudaMemsetAsync(output->ptr, 0, static_cast<size_t>(M) * N * 2, stream));
+    const size_t count = static_cast<size_t>(M) * N;
+    if (bias == 0.0f) {
+      CROQ_CUDA_TRY(cudaMemsetAsync(output->ptr, 0, count * out_elem, stream));
+    } else {
+      fill_bias_kernel<<<st->sm_count * 4, 256, 0, stream>>>(output->ptr, count, out_kind, bias);
+      CROQ_CUDA_TRY(cudaGetLastError());
+    }
     return CROQ_OK;
   }
   DenseParams p;
   p.out = static_cast<uint16_t*>(output->ptr);
+  p.out_ex = output->ptr;
+  p.ld_out = transposed ? static_cast<size_t>(M) : static_cast<size_t>(N);
+  p.epi_plain = plain ? 1 : 0;
+  p.out_kind = out_kind;
+  p.transposed = transposed ? 1 : 0;
+  p.bias = bias;
   p.M = M; p.N = N; p.K = K;
   p.sched_m = schedule_m ? static_cast<const int*>(schedule_m->ptr) : nullptr;
   p.sched_n = schedule_n ? static_cast<const int*>(schedule_n->ptr) : nullptr;
@@ -508,14 +561,28 @@ int croq_matmul_f16(const croq_view2* lhs, const croq_view2* rhs, const croq_vie
                     const croq_view1* schedule_m, const croq_view1* schedule_n,
                     int sched_tile_m, int sched_tile_n, croq_stream stream) {
   return croq::launch_dense<false>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
-                                   sched_tile_n, stream);
+                                   sched_tile_n, nullptr, stream);
 }
 
 int croq_matmul_bf16(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
                      const croq_view1* schedule_m, const croq_view1* schedule_n,
                      int sched_tile_m, int sched_tile_n, croq_stream stream) {
   return croq::launch_dense<true>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
-                                  sched_tile_n, stream);
+                                  sched_tile_n, nullptr, stream);
+}
+
+int croq_matmul_ex(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                   const croq_view1* schedule_m, const croq_view1* schedule_n, int sched_tile_m,
+                   int sched_tile_n, int in_dtype, const croq_epilogue* epilogue,
+                   croq_stream stream) {
+  if (in_dtype == CROQ_DTYPE_F16)
+    return croq::launch_dense<false>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
+                                     sched_tile_n, epilogue, stream);
+  if (in_dtype == CROQ_DTYPE_BF16)
+    return croq::launch_dense<true>(lhs, rhs, output, schedule_m, schedule_n, sched_tile_m,
+                                    sched_tile_n, epilogue, stream);
+  croq::clear_error();
+  return CROQ_ERR_UNSUPPORTED;
 }
 
 }  // extern "C"

@@ -48,7 +48,7 @@ enum {
   CROQ_ERR_NO_DEVICE = 9     /* no sm_100 device is current */
 };
 
-enum { CROQ_DTYPE_F16 = 0, CROQ_DTYPE_BF16 = 1 };
+enum { CROQ_DTYPE_F16 = 0, CROQ_DTYPE_BF16 = 1, CROQ_DTYPE_F32 = 2 };
 
 const char* croq_status_string(int status);
 /* Text of the last CUDA error seen by the calling thread ("" if none). */
@@ -87,6 +87,28 @@ int croq_matmul_bf16(const croq_view2* lhs, const croq_view2* rhs, const croq_vi
                      const croq_view1* schedule_m, const croq_view1* schedule_n,
                      int sched_tile_m, int sched_tile_n, croq_stream stream);
 
+/* The same GEMM with the epilogue variants the reference exposes on
+ * `mma.store`:
+ *   out_dtype   CROQ_DTYPE_F16 / _BF16 / _F32 — f32 output as in `matmul_e4m3`'s
+ *               `global f32 [M,N] output` (tests/gpu/end2end/wgmma_ss.co:5-28);
+ *   transposed  non-zero: output is [N,M] and element (m,n) lands at
+ *               output[n,m] — `mma.store.transp` (wgmma_ss.co:146-166);
+ *   bias        scalar added to every accumulator before rounding — `mc += bias`
+ *               (tests/gpu/end2end/ampere_mma.co:79-104).
+ * Ragged M and N need no flag (`mma.store.mask`, wgmma_ss.co:169-194: stores
+ * are always clipped to the output extents). in_dtype is the element type of
+ * lhs and rhs (CROQ_DTYPE_F16 or _BF16). epilogue == NULL is croq_matmul_f16 /
+ * croq_matmul_bf16. */
+typedef struct croq_epilogue {
+  int out_dtype;
+  int transposed;
+  float bias;
+} croq_epilogue;
+int croq_matmul_ex(const croq_view2* lhs, const croq_view2* rhs, const croq_view2* output,
+                   const croq_view1* schedule_m, const croq_view1* schedule_n,
+                   int sched_tile_m, int sched_tile_n, int in_dtype,
+                   const croq_epilogue* epilogue, croq_stream stream);
+
 /* FP8 e4m3 GEMM with fp32 block scales.
  * Replaces `__co__ blockscale_gemm_e4m3_ws_persis(lhs, scale_lhs, rhs,
  * scale_rhs, output)` (wgmma_persis.co:94-154) in its fp32-accumulator form
@@ -101,6 +123,17 @@ int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2* scale_lhs
                               const croq_view2* rhs, const croq_view2* scale_rhs,
                               const croq_view2* output, int out_dtype, croq_stream stream);
 
+/* The same GEMM with scale_lhs stored K-major, f32 [cdiv(K,128), M]
+ * (CROQ_SCALE_K_MAJOR): the `[1, M_tile]` scale view the reference's
+ * `mma.scale` accepts beside `[M_tile, 1]` (lib/semacheck.cpp:1481-1486,
+ * lib/Target/GPU/cute_codegen.cpp:6467-6473). The 32 rows a warp promotes then
+ * read 32 consecutive scales. CROQ_SCALE_ROW_MAJOR is croq_blockscale_gemm_e4m3. */
+enum { CROQ_SCALE_ROW_MAJOR = 0, CROQ_SCALE_K_MAJOR = 1 };
+int croq_blockscale_gemm_e4m3_ex(const croq_view2* lhs, const croq_view2* scale_lhs,
+                                 const croq_view2* rhs, const croq_view2* scale_rhs,
+                                 const croq_view2* output, int out_dtype, int scale_lhs_layout,
+                                 croq_stream stream);
+
 /* 2:4 structured-sparse f16 GEMM.
  * Replaces the sparse `__co__` kernels of tests/gpu/end2end/gemm_sp.co:101-290:
  *   output = dense(lhs_packed, lhs_meta) * rhs^T, fp32 accumulation.
@@ -111,6 +144,25 @@ int croq_blockscale_gemm_e4m3(const croq_view2* lhs, const croq_view2* scale_lhs
 int croq_gemm_sp_f16(const croq_view2* lhs_packed, const croq_view2* lhs_meta,
                      const croq_view2* rhs, const croq_view2* output, int out_dtype,
                      croq_stream stream);
+
+/* 2:4 compressor on the GPU. Replaces the host loop
+ * Sparse2to4HostPolicyWGMMA::encode (runtime/choreo.h:1536-1571): dense [M,K]
+ * of 16-bit values (f16 or bf16; "non-zero" is everything but +-0) with at most
+ * two non-zeros per group of four K positions -> packed [M,K/2] and lhs_meta
+ * u8 [M,K/8] as croq_gemm_sp_f16 takes them. A group that does not hold exactly
+ * two non-zeros keeps positions 0 and 1, like the reference. K % 8 == 0. */
+int croq_sparse24_encode_f16(const croq_view2* dense, const croq_view2* packed,
+                             const croq_view2* meta_u8, croq_stream stream);
+
+/* Metadata re-layout for interchange with the reference's Hopper kernels:
+ * u8 [M,K/8] -> u32 [M,K/32]. CROQ_SPARSE_META_PREPACK replaces
+ * Sparse2to4HostPolicyWGMMA::prepack (runtime/choreo.h:1573-1623),
+ * CROQ_SPARSE_META_PREPACK_V2 replaces ::prepack_v2 (1631-1661; the words of a
+ * 16-row block and K fragment contiguous, [M/16, K/32, 16]). M % 16 == 0 and
+ * K % 32 == 0, as the reference asserts. */
+enum { CROQ_SPARSE_META_PREPACK = 1, CROQ_SPARSE_META_PREPACK_V2 = 2 };
+int croq_sparse24_prepack_meta(const croq_view2* meta_u8, const croq_view2* meta_u32, int layout,
+                               croq_stream stream);
 
 /* ---- MoE path. The reference has no counterpart for these entry points; the
  * argument conventions follow the spanned-view rules above. ---- */

@@ -255,6 +255,35 @@ ORACLE_API void oracle_sparse24_decode_u16(const uint16_t* packed, const uint8_t
     }
 }
 
+/* Metadata re-layouts for the reference's Hopper kernels. `layout` 1 restates
+ * Sparse2to4HostPolicyWGMMA::prepack (runtime/choreo.h:1573-1623): for every
+ * 16-row block, row r in 0..7 and 32-wide K fragment kf (4 metadata bytes per
+ * row), word (block+2r, kf) = bytes 0,1 of row block+r in the low half and
+ * bytes 0,1 of row block+r+8 in the high half, word (block+2r+1, kf) the same
+ * for bytes 2,3. `layout` 2 restates prepack_v2 (1631-1661): the same words
+ * stored as [M/16, KF, 16]. M % 16 == 0, KM % 4 == 0. Returns 0, or -1 on a
+ * shape the reference asserts against. */
+ORACLE_API int oracle_sparse24_prepack_meta(const uint8_t* meta_u8, uint32_t* meta_u32, int M,
+                                            int KM, int layout) {
+  if (M % 16 != 0 || KM % 4 != 0 || (layout != 1 && layout != 2)) return -1;
+  const int KF = KM / 4;
+  for (int block = 0; block < M; block += 16)
+    for (int r = 0; r < 8; ++r)
+      for (int kf = 0; kf < KF; ++kf)
+        for (int h = 0; h < 2; ++h) {
+          const uint8_t* lo = meta_u8 + (size_t)(block + r) * KM + kf * 4 + 2 * h;
+          const uint8_t* hi = meta_u8 + (size_t)(block + r + 8) * KM + kf * 4 + 2 * h;
+          const uint32_t word = (uint32_t)lo[0] | ((uint32_t)lo[1] << 8) |
+                                ((uint32_t)hi[0] << 16) | ((uint32_t)hi[1] << 24);
+          const int rib = 2 * r + h;
+          const size_t at = (layout == 1)
+              ? (size_t)(block + rib) * KF + kf
+              : ((size_t)(block / 16) * KF + kf) * 16 + rib;
+          meta_u32[at] = word;
+        }
+  return 0;
+}
+
 /* --------------------------------------------------------- Hilbert schedule --
  * Restates build_hilbert_schedule (tests/gpu/end2end/wgmma_persis.co:156-197):
  * walk the Hilbert curve over the covering power-of-two square, keep cells

@@ -162,6 +162,20 @@ def sparse24_decode(packed_bits: np.ndarray, meta: np.ndarray) -> np.ndarray:
     return dense
 
 
+def sparse24_prepack_meta(meta: np.ndarray, layout: int) -> np.ndarray:
+    """u8 [M,K/8] metadata -> u32 [M,K/32] in the reference's `prepack` (layout 1) or
+    `prepack_v2` (layout 2) order."""
+    m = _c(meta, np.uint8)
+    M, KM = m.shape
+    out = np.zeros((M, KM // 4), np.uint32)
+    fn = lib().oracle_sparse24_prepack_meta
+    fn.restype = c_int
+    fn.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
+    if fn(_p(m), _p(out), M, KM, layout) != 0:
+        raise ValueError("prepack needs M % 16 == 0, K/8 % 4 == 0, layout 1 or 2")
+    return out
+
+
 # ----------------------------------------------------------------- schedule --
 
 def hilbert_schedule(tiles_m: int, tiles_n: int):

@@ -45,6 +45,18 @@ __attribute__((visibility("default"))) void ref_sparse24_encode_f32(
   std::memcpy(meta, m.data(), (size_t)M * (K / 8));
 }
 
+// Sparse2to4HostPolicyWGMMA<float,64>::prepack (layout 1, runtime/choreo.h:1573-1623)
+// and ::prepack_v2 (layout 2, 1631-1661) on u8 metadata [M, KM].
+__attribute__((visibility("default"))) void ref_sparse24_prepack_meta(
+    const uint8_t* meta_u8, uint32_t* meta_u32, int M, int KM, int layout) {
+  auto in = choreo::make_spandata<choreo::u8>((size_t)M, (size_t)KM);
+  auto out = choreo::make_spandata<choreo::u32>((size_t)M, (size_t)KM / 4);
+  std::memcpy(in.data(), meta_u8, (size_t)M * KM);
+  if (layout == 1) choreo::utils::Sparse2to4HostPolicyWGMMA<float, 64>::prepack(in, out);
+  else choreo::utils::Sparse2to4HostPolicyWGMMA<float, 64>::prepack_v2(in, out);
+  std::memcpy(meta_u32, out.data(), sizeof(uint32_t) * (size_t)M * (KM / 4));
+}
+
 // Sparse2to4HostPolicyWGMMA<float,64>::init_structured_sparse_A with
 // std::mt19937(seed) (runtime/choreo.h:1508-1537; the sparse tests seed 42,
 // tests/gpu/end2end/gemm_sp.co:296-334), followed by the test's B recipe

@@ -139,10 +139,20 @@ def main() -> None:
     pk2 = np.zeros(irr.size // 2, np.float32)
     meta2 = np.zeros(irr.size // 8, np.uint8)
     ref.ref_sparse24_encode_f32(p(irr), p(pk2), p(meta2), 16, 32)
+    # metadata re-layouts of the reference (prepack, prepack_v2) on the seed-42 metadata and
+    # on random bytes (48 rows x 12 bytes: three 16-row blocks, three K fragments)
+    ref.ref_sparse24_prepack_meta.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
+    rnd_meta = rng.integers(0, 256, 48 * 12, dtype=np.uint8)
+    pre = {}
+    for tag, mm, rows, km in (("kat", meta, Ms, Ks // 8), ("rnd", rnd_meta, 48, 12)):
+        for layout in (1, 2):
+            o = np.zeros(rows * km // 4, np.uint32)
+            ref.ref_sparse24_prepack_meta(p(mm), p(o), rows, km, layout)
+            pre[f"{tag}_prepack_v{layout}"] = o.reshape(rows, km // 4)
     np.savez_compressed(OUT / "sparse.npz", dense_a=da.reshape(Ms, Ks), rhs=rb.reshape(Ns, Ks),
                         packed=pk.reshape(Ms, Ks // 2), meta=meta.reshape(Ms, Ks // 8),
                         irr_dense=irr.reshape(16, 32), irr_packed=pk2.reshape(16, 16),
-                        irr_meta=meta2.reshape(16, 4))
+                        irr_meta=meta2.reshape(16, 4), rnd_meta=rnd_meta.reshape(48, 12), **pre)
 
     # ---- sampled-verifier stride -----------------------------------------
     ref.ref_pick_coprime_stride.restype = c_size_t

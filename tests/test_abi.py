@@ -74,6 +74,29 @@ def test_argument_checks_run_before_any_cuda_call(croq):
     assert bs(ok[0], ok[1], ok[2], v2(P, 3, 2), ok[4], 1, None) == 2       # scale_rhs [N/128, K/128]
     assert bs(ok[0], ok[1], ok[2], ok[3], ok[4], 7, None) == 8             # out dtype
     assert bs(ok[0], ok[1], ok[2], ok[3], None, 1, None) == 1
+    bx = croq.croq_blockscale_gemm_e4m3_ex
+    # K-major [K/128, M] passes the shape check: the next check (output alignment) is the one that fails
+    assert bx(ok[0], v2(P, 2, 128), ok[2], ok[3], v2(P + 1, 128, 256), 1, 1, None) == 3
+    assert bx(ok[0], ok[1], ok[2], ok[3], ok[4], 1, 1, None) == 2          # row-major shape with the K-major flag
+    assert bx(ok[0], ok[1], ok[2], ok[3], ok[4], 1, 5, None) == 8          # unknown layout
+    from croqtile_b200._lib import Epilogue
+    mx = croq.croq_matmul_ex
+    epi = lambda d, t: ctypes.byref(Epilogue(d, t, 0.0))
+    good = (v2(P, 64, 32), v2(P, 48, 32))
+    assert mx(good[0], good[1], v2(P, 64, 48), None, None, 256, 256, 0, epi(7, 0), None) == 8   # out dtype
+    assert mx(good[0], good[1], v2(P, 64, 48), None, None, 256, 256, 2, None, None) == 8        # in dtype
+    assert mx(good[0], good[1], v2(P, 64, 48), None, None, 256, 256, 0, epi(2, 1), None) == 2   # transposed: [N,M]
+    assert mx(good[0], good[1], v2(P + 2, 64, 48), None, None, 256, 256, 0, epi(2, 0), None) == 3  # f32 alignment
+    enc = croq.croq_sparse24_encode_f16
+    assert enc(v2(P, 16, 64), v2(P, 16, 32), None, None) == 1
+    assert enc(v2(P, 16, 60), v2(P, 16, 30), v2(P, 16, 7), None) == 2       # K % 8
+    assert enc(v2(P, 16, 64), v2(P, 16, 32), v2(P, 16, 4), None) == 2       # meta [M, K/8]
+    assert enc(v2(P + 4, 16, 64), v2(P, 16, 32), v2(P, 16, 8), None) == 3   # 16-byte loads
+    pre = croq.croq_sparse24_prepack_meta
+    assert pre(v2(P, 16, 8), v2(P, 16, 2), 3, None) == 8                    # unknown layout
+    assert pre(v2(P, 24, 8), v2(P, 24, 2), 1, None) == 2                    # M % 16 (choreo.h:1583)
+    assert pre(v2(P, 16, 6), v2(P, 16, 1), 1, None) == 2                    # K/8 % 4
+    assert pre(v2(P, 16, 8), v2(P, 16, 3), 2, None) == 2                    # one word per fragment
 
 
 def test_loader_fails_loudly_when_library_is_missing(monkeypatch, tmp_path):

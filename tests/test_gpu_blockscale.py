@@ -108,3 +108,22 @@ def test_config3_full_size_sampled_rows(oracle, shape):
     got_sum = out.double().sum(1)
     scale = (deq_a.abs() @ colsum.abs()).clamp_min(1.0)
     assert ((got_sum - want).abs() / scale).max().item() < 2e-3
+
+
+@pytest.mark.parametrize("shape", [(256, 384, 1024), (200, 136, 272), (513, 1000, 400)])
+def test_k_major_lhs_scales_give_identical_bits(oracle, shape):
+    """scale_lhs stored [K/128, M] (the `[1, M_tile]` view mma.scale accepts,
+    lib/semacheck.cpp:1481-1486): same arithmetic, so the output bits equal the
+    row-major call's, on the single-CTA (M <= 128 rows per tile) and pair kernels."""
+    m, n, k = shape
+    rng = np.random.default_rng(m * 7 + k)
+    a, sa = oracle.quant_rows_e4m3(rng.standard_normal((m, k)).astype(np.float32))
+    b, sb = oracle.quant_blocks_e4m3(rng.standard_normal((n, k)).astype(np.float32))
+    a_d, b_d, sb_d = to_dev_e4m3(a), to_dev_e4m3(b), to_dev(sb)
+    row_major = api.blockscale_gemm_e4m3(a_d, to_dev(sa), b_d, sb_d, poisoned((m, n), "bf16"))
+    k_major = api.blockscale_gemm_e4m3(a_d, to_dev(np.ascontiguousarray(sa.T)), b_d, sb_d,
+                                       poisoned((m, n), "bf16"), scale_lhs_k_major=True)
+    api.synchronize()
+    np.testing.assert_array_equal(bits_of(k_major), bits_of(row_major))
+    ref = oracle.blockscale_gemm_e4m3(a, sa, b, sb)
+    assert max_rel_err(oracle.decode(bits_of(k_major), "bf16"), ref, floor=0.05 * np.sqrt(k)) <= REL_TOL

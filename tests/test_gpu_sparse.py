@@ -108,3 +108,52 @@ def test_config4_full_size_sampled_rows(oracle):
     got = oracle.f16_to_f32(bits_of(out[torch.from_numpy(rows).cuda()]))
     assert max_rel_err(got, ref, floor=0.05 * np.sqrt(n)) <= 5e-3
     assert torch.isfinite(out.float()).all()
+
+
+def test_gpu_compressor_matches_reference_encoder(oracle, golden):
+    """croq_sparse24_encode_f16 against the reference encoder's bytes (golden: seed-42 case
+    and an irregular case with 0, 1, 3 and 4 non-zeros per group), then against the oracle
+    on a larger random matrix that also holds -0, NaN and subnormals."""
+    g = golden["sparse"]
+    for dense, packed, meta in [(g["dense_a"], g["packed"], g["meta"]),
+                                (g["irr_dense"], g["irr_packed"], g["irr_meta"])]:
+        bits = oracle.f32_to_f16(dense)
+        p_dev, m_dev = api.sparse24_encode(to_dev_16(bits, "f16"))
+        np.testing.assert_array_equal(bits_of(m_dev), meta)
+        np.testing.assert_array_equal(bits_of(p_dev), oracle.f32_to_f16(packed))
+    rng = np.random.default_rng(77)
+    bits = rng.integers(0, 1 << 16, (257, 520), dtype=np.uint16)     # ragged M, K % 8 == 0
+    bits[rng.random(bits.shape) < 0.5] = 0
+    bits[rng.random(bits.shape) < 0.05] = 0x8000                     # -0 is a zero
+    bits[3, :8] = [0x7E00, 0, 0, 0x0001, 0x8000, 0xFC00, 0x0001, 0]  # NaN, subnormal, -inf
+    for dtype in ("f16", "bf16"):
+        p_dev, m_dev = api.sparse24_encode(to_dev_16(bits, dtype))
+        p_ref, m_ref = oracle.sparse24_encode(bits)
+        np.testing.assert_array_equal(bits_of(m_dev), m_ref)
+        np.testing.assert_array_equal(bits_of(p_dev), p_ref)
+
+
+def test_gpu_compressor_feeds_the_sparse_gemm(oracle):
+    """dense 2:4 matrix -> GPU compressor -> sparse GEMM equals the dense product."""
+    M, N, K = 384, 256, 512
+    rng = np.random.default_rng(5)
+    dense = random_24(rng, M, K)
+    rhs = (rng.random((N, K)) * 2 - 1).astype(np.float32)
+    bits, rb = oracle.f32_to_f16(dense), oracle.f32_to_f16(rhs)
+    p_dev, m_dev = api.sparse24_encode(to_dev_16(bits, "f16"))
+    out = api.gemm_sp_f16(p_dev, m_dev, to_dev_16(rb, "f16"), poisoned((M, N), "f16"))
+    api.synchronize()
+    ref = oracle.gemm_row_row(oracle.f16_to_f32(bits), oracle.f16_to_f32(rb))
+    assert max_rel_err(oracle.f16_to_f32(bits_of(out)), ref, floor=0.05 * np.sqrt(K)) <= 5e-3
+
+
+def test_gpu_metadata_prepack_matches_reference(oracle, golden):
+    g = golden["sparse"]
+    for tag, meta in (("kat", g["meta"]), ("rnd", g["rnd_meta"])):
+        for layout in (1, 2):
+            got = api.sparse24_prepack_meta(to_dev(meta), layout).cpu().numpy().view(np.uint32)
+            np.testing.assert_array_equal(got, g[f"{tag}_prepack_v{layout}"])
+    meta = np.random.default_rng(9).integers(0, 256, (8192, 1024), dtype=np.uint8)   # config 4
+    for layout in (1, 2):
+        got = api.sparse24_prepack_meta(to_dev(meta), layout).cpu().numpy().view(np.uint32)
+        np.testing.assert_array_equal(got, oracle.sparse24_prepack_meta(meta, layout))

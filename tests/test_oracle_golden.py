@@ -103,6 +103,18 @@ def test_kat1_mod3_pattern(oracle, golden):
     np.testing.assert_array_equal(bs, out)
 
 
+def test_sparse_metadata_prepack_matches_reference(oracle, golden):
+    """prepack / prepack_v2 (runtime/choreo.h:1573-1661) on the seed-42 metadata and on
+    random bytes; the golden words come from the reference's own functions."""
+    g = golden["sparse"]
+    for tag, meta in (("kat", g["meta"]), ("rnd", g["rnd_meta"])):
+        for layout in (1, 2):
+            np.testing.assert_array_equal(oracle.sparse24_prepack_meta(meta, layout),
+                                          g[f"{tag}_prepack_v{layout}"])
+    with pytest.raises(ValueError):
+        oracle.sparse24_prepack_meta(np.zeros((8, 4), np.uint8), 1)     # M % 16
+
+
 def test_sparse_encoder_matches_reference(oracle, golden):
     g = golden["sparse"]
     for dense, packed, meta in [(g["dense_a"], g["packed"], g["meta"]),
