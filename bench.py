@@ -45,7 +45,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the
 # ncu captures summarised under profiles/ (same command, same shapes)
 NCU_DRAM_TRAFFIC_BYTES = {
-    "fp8_blockscale_8192": 338.76e6 + 113.34e6,
+    "fp8_blockscale_8192": 350.80e6 + 118.65e6,
     "bf16_hilbert_8192": 1.1129e9 + 128.0e6,
     "sparse24_f16_8192": 709.02e6 + 122.42e6,
 }
@@ -422,16 +422,55 @@ def run_croq_arm(args, kind, M, N, K):
                                 f"bf16 cuBLAS burst {bf16_peak} TFLOP/s"),
                 "frac_of_nominal": achieved / NOMINAL_PEAK_TFLOPS[kind],
                 "nominal_peak": NOMINAL_PEAK_TFLOPS[kind],
-                "kernel": {"blockscale": "gemm_blockscale_kernel", "sparse": "gemm_sparse_kernel"}.get(
+                "kernel": {"blockscale": "gemm_blockscale_pair_kernel", "sparse": "gemm_sparse_pair_kernel"}.get(
                     kind, "gemm_dense_pair_kernel"),
                 "launch_ms_mean": launch_ms, "launch_ms_min": float(per_step.min()),
             },
         }
+        if kind == "sparse" and world == 1:
+            line["kernels"] = sparse_tool_kernels(api, torch, *sets[0]["args"][:2], hbm)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_line(kind, M, N, K)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sparse_tool_kernels(api, torch, vals, meta, hbm_peak):
+    """The HBM-bound 2:4 tooling beside the sparse GEMM, timed with CUDA events outside
+    the step loop: the compressor (dense [M,K] -> packed + metadata) and the two metadata
+    re-layouts. The dense input is rebuilt from the workload's (packed, metadata), so the
+    compressor's output must reproduce them bit for bit."""
+    M, K = vals.shape[0], vals.shape[1] * 2
+    nib = torch.stack((meta & 15, meta >> 4), dim=-1).view(M, K // 4)
+    dense = torch.zeros((M, K // 4, 4), dtype=vals.dtype, device=vals.device)
+    v = vals.view(M, K // 4, 2)
+    dense.scatter_(2, (nib & 3).long().unsqueeze(-1), v[..., :1])
+    dense.scatter_(2, ((nib >> 2) & 3).long().unsqueeze(-1), v[..., 1:])
+    dense = dense.view(M, K)
+    del nib
+    packed, meta2 = api.sparse24_encode(dense)
+    if not (torch.equal(packed, vals) and torch.equal(meta2, meta)):
+        raise SystemExit("2:4 compressor does not reproduce the workload's operands")
+
+    def timed(fn, nbytes, reps=10):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm_peak}
+
+    return {
+        "sparse24_encode": timed(lambda: api.sparse24_encode(dense), M * K * 2 + M * K + M * K // 8),
+        "sparse24_prepack": timed(lambda: api.sparse24_prepack_meta(meta, 1), 2 * (M * K // 8)),
+        "sparse24_prepack_v2": timed(lambda: api.sparse24_prepack_meta(meta, 2), 2 * (M * K // 8)),
+    }
 
 
 

@@ -134,6 +134,61 @@ inline int gemm_sp_f16(const VP& lhs_packed, const VM& lhs_meta, const VB& rhs, 
   return detail::finish(croq_gemm_sp_f16(&p, &m, &b, &c, CROQ_DTYPE_F16, stream), stream, "gemm_sp_f16");
 }
 
+// `__co__ void matmul_st_trans(global f16 [M,K] lhs, global f16 [N,K] rhs, global f16 [N,M]
+//  output)` (tests/gpu/end2end/wgmma_ss.co:146-166): `mma.store.transp`.
+template <class VA, class VB, class VC>
+inline int matmul_st_trans(const VA& lhs, const VB& rhs, const VC& output,
+                           croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  const croq_epilogue epi = {CROQ_DTYPE_F16, 1, 0.0f};
+  return detail::finish(croq_matmul_ex(&a, &b, &c, nullptr, nullptr, 256, 256, CROQ_DTYPE_F16, &epi, stream),
+                        stream, "matmul_st_trans");
+}
+
+// `__co__ void matmul_st_masked(lhs, rhs, output)` (wgmma_ss.co:169-194): `mma.store.mask`
+// with row_guard / col_guard. Every store of the library is clipped to the
+// output extents, so this is the plain call on ragged M and N.
+template <class VA, class VB, class VC>
+inline int matmul_st_masked(const VA& lhs, const VB& rhs, const VC& output,
+                            croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  return detail::finish(croq_matmul_f16(&a, &b, &c, nullptr, nullptr, 256, 256, stream), stream,
+                        "matmul_st_masked");
+}
+
+// f16 operands, f32 output [M,N] (the `global f32 [M, N] output` store of
+// wgmma_ss.co:5-28) and/or the scalar fusion `mc += bias` of
+// tests/gpu/end2end/ampere_mma.co:79-104.
+template <class VA, class VB, class VC>
+inline int matmul_f16_epilogue(const VA& lhs, const VB& rhs, const VC& output, int out_dtype,
+                               float bias = 0.0f, croq_stream stream = nullptr) {
+  croq_view2 a = detail::v2(lhs), b = detail::v2(rhs), c = detail::v2(output);
+  const croq_epilogue epi = {out_dtype, 0, bias};
+  return detail::finish(croq_matmul_ex(&a, &b, &c, nullptr, nullptr, 256, 256, CROQ_DTYPE_F16, &epi, stream),
+                        stream, "matmul_f16_epilogue");
+}
+
+// Device-side forms of choreo::utils::Sparse2to4HostPolicyWGMMA<T,K>::encode,
+// ::prepack and ::prepack_v2 (runtime/choreo.h:1536-1661), same argument order.
+template <class VD, class VP, class VM>
+inline int sparse24_encode(const VD& dense, const VP& packed, const VM& meta,
+                           croq_stream stream = nullptr) {
+  croq_view2 d = detail::v2(dense), p = detail::v2(packed), m = detail::v2(meta);
+  return detail::finish(croq_sparse24_encode_f16(&d, &p, &m, stream), stream, "sparse24_encode");
+}
+template <class VM, class VW>
+inline int sparse24_prepack(const VM& meta_u8, const VW& meta_u32, croq_stream stream = nullptr) {
+  croq_view2 m = detail::v2(meta_u8), w = detail::v2(meta_u32);
+  return detail::finish(croq_sparse24_prepack_meta(&m, &w, CROQ_SPARSE_META_PREPACK, stream), stream,
+                        "sparse24_prepack");
+}
+template <class VM, class VW>
+inline int sparse24_prepack_v2(const VM& meta_u8, const VW& meta_u32, croq_stream stream = nullptr) {
+  croq_view2 m = detail::v2(meta_u8), w = detail::v2(meta_u32);
+  return detail::finish(croq_sparse24_prepack_meta(&m, &w, CROQ_SPARSE_META_PREPACK_V2, stream), stream,
+                        "sparse24_prepack_v2");
+}
+
 }  // namespace croq_b200
 
 #endif  // CROQ_B200_HPP_

@@ -23,6 +23,14 @@ int main() {
   // null data pointers: the entry point must answer CROQ_ERR_NULL without touching CUDA
   int rc = croq_b200::matmul_persis_hilbert_sm90(lhs, rhs, out, sm, sn);
   std::printf("rc=%%d %%s\n", rc, croq_status_string(rc));
+  // the store variants and the sparse tooling keep the same rule
+  %(view_f16)s out_t{%(null_f16)s, {48, 64}};
+  if (croq_b200::matmul_st_trans(lhs, rhs, out_t) != CROQ_ERR_NULL) return 2;
+  if (croq_b200::matmul_st_masked(lhs, rhs, out) != CROQ_ERR_NULL) return 3;
+  if (croq_b200::matmul_f16_epilogue(lhs, rhs, out, CROQ_DTYPE_F32, 0.5f) != CROQ_ERR_NULL) return 4;
+  if (croq_b200::sparse24_encode(lhs, rhs, out) != CROQ_ERR_NULL) return 5;
+  if (croq_b200::sparse24_prepack(lhs, out) != CROQ_ERR_NULL) return 6;
+  if (croq_b200::sparse24_prepack_v2(lhs, out) != CROQ_ERR_NULL) return 7;
   return rc == CROQ_ERR_NULL ? 0 : 1;
 }
 '''
