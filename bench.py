@@ -605,7 +605,9 @@ def run_moe_arm(args, T, H, I):
             return a.elapsed_time(b) / reps, out
         rows = T * k
         ms_route, r = timed(lambda: api.moe_route_topk(lg[0], k))
-        ms_pq, (xq, xsc) = timed(lambda: api.moe_permute_quant_e4m3(xs[0], r["perm_to_src"], k))
+        ms_pq_fused, _ = timed(lambda: api.moe_permute_quant_e4m3(xs[0], r["perm_to_src"], k))
+        ms_q0, (xq0, xs0) = timed(lambda: api.quant_rows_e4m3(xs[0]))
+        ms_pq, (xq, xsc) = timed(lambda: api.moe_permute_q_e4m3(xq0, xs0, r["perm_to_src"], k))
         ms_g1, gact = timed(lambda: api.moe_grouped_gemm_e4m3(xq, xsc, w13, w13s, r["expert_offsets"], swiglu=True))
         ms_q, (gq, gs) = timed(lambda: api.quant_rows_e4m3(gact))
         ms_g2, y = timed(lambda: api.moe_grouped_gemm_e4m3(gq, gs, w2, w2s, r["expert_offsets"]))
@@ -617,7 +619,10 @@ def run_moe_arm(args, T, H, I):
             return {"ms": ms, "algorithmic_bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm}
         kernels = {
             "route_topk": bw(T * E * 4 + rows * 8 + (2 * E + 1) * 4 + 2 * rows * 4, ms_route),
-            "permute_quant": bw(rows * (2 * H + H + 4 * H // 128) + rows * 4, ms_pq),
+            "quant_tokens": bw(T * (2 * H + H + 4 * H // 128), ms_q0),
+            "permute_quantised_rows": bw(2 * rows * (H + 4 * H // 128) + rows * 4, ms_pq),
+            "permute_quant_fused (not on the layer's path)": bw(rows * (2 * H + H + 4 * H // 128) + rows * 4,
+                                                               ms_pq_fused),
             "grouped_gemm_gate_up_swiglu": {"ms": ms_g1, "TFLOP/s": 2.0 * rows * 2 * I * H / (ms_g1 * 1e-3) / 1e12},
             "quant_rows": bw(rows * (2 * I + I + 4 * I // 128), ms_q),
             "grouped_gemm_down": {"ms": ms_g2, "TFLOP/s": 2.0 * rows * H * I / (ms_g2 * 1e-3) / 1e12},
@@ -643,7 +648,7 @@ def run_moe_arm(args, T, H, I):
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": t_loc * (H * 2 + E * 4),
                     "d2h_bytes_per_step": t_loc * H * 2, "steps": e2e_steps},
-            "gpu_launches": args.steps * (8 if world == 1 else 14),
+            "gpu_launches": args.steps * (9 if world == 1 else 15),
         }
         if phases is not None:
             line["phases_ms_rank0"] = phases

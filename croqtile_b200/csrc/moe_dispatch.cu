@@ -90,6 +90,72 @@ moe_dispatch_quant_kernel(const uint16_t* __restrict__ src, const int* __restric
   }
 }
 
+// Dispatch of rows that were quantised once per token beforehand: a pure copy
+// of H e4m3 bytes and H/128 scales per expanded row into the owner's buffers,
+// 16-byte peer stores. Same placement rule as above; a CTA moves kRows rows and
+// issues all its loads before the first store.
+template <int kRows>
+__global__ void __launch_bounds__(kRowThreads)
+moe_dispatch_rows_q_kernel(const uint8_t* __restrict__ q_src, const float* __restrict__ s_src,
+                           const int* __restrict__ perm_to_src, const int* __restrict__ topk_idx,
+                           const int* __restrict__ expert_offsets, const int* __restrict__ dest_base,
+                           const unsigned long long* __restrict__ peer_q,
+                           const unsigned long long* __restrict__ peer_scale, int k, int T, int E,
+                           int rows, int experts_per_rank, int capacity_rows, int H, int SB,
+                           int* __restrict__ status) {
+  const int pos0 = blockIdx.x * kRows;
+  const uint8_t* src_q[kRows];
+  const float* src_s[kRows];
+  uint8_t* dst_q[kRows];
+  float* dst_s[kRows];
+  bool live[kRows];
+#pragma unroll
+  for (int j = 0; j < kRows; ++j) {
+    const int pos = pos0 + j;
+    live[j] = false;
+    src_q[j] = q_src; src_s[j] = s_src; dst_q[j] = nullptr; dst_s[j] = nullptr;
+    if (pos >= rows) continue;
+    const int r = perm_to_src[pos];
+    const int t = r / k;
+    bool ok = r >= 0 && t < T;
+    int e = 0, dest_row = 0;
+    if (ok) {
+      e = topk_idx[r];
+      ok = e >= 0 && e < E;
+    }
+    if (ok) {
+      dest_row = dest_base[e] + (pos - expert_offsets[e]);
+      ok = dest_row >= 0 && dest_row < capacity_rows;   // else: owner's buffer too small
+    }
+    if (!ok) {
+      if (threadIdx.x == 0) *status = kDevBadIndex;
+      continue;
+    }
+    const int owner = e / experts_per_rank;
+    live[j] = true;
+    src_q[j] = q_src + static_cast<size_t>(t) * H;
+    src_s[j] = s_src + static_cast<size_t>(t) * SB;
+    dst_q[j] = reinterpret_cast<uint8_t*>(peer_q[owner]) + static_cast<size_t>(dest_row) * H;
+    dst_s[j] = reinterpret_cast<float*>(peer_scale[owner]) + static_cast<size_t>(dest_row) * SB;
+  }
+  const int chunks = H / 16;
+  for (int c = threadIdx.x; c < chunks; c += kRowThreads) {
+    uint4 v[kRows];
+#pragma unroll
+    for (int j = 0; j < kRows; ++j)
+      v[j] = live[j] ? __ldg(reinterpret_cast<const uint4*>(src_q[j]) + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < kRows; ++j)
+      if (live[j]) reinterpret_cast<uint4*>(dst_q[j])[c] = v[j];
+  }
+  for (int i = threadIdx.x; i < SB * kRows; i += kRowThreads) {
+    const int r = i / SB, c = i - r * SB;
+#pragma unroll
+    for (int j = 0; j < kRows; ++j)
+      if (j == r && live[j]) dst_s[j][c] = __ldg(src_s[j] + c);
+  }
+}
+
 // out[t,:] = RN_bf16( sum_j w[t,j] * y_owner(t,j)[row(t,j), :] ), ascending j.
 template <int kMaxK>
 __global__ void __launch_bounds__(kRowThreads)
@@ -187,6 +253,46 @@ int croq_moe_dispatch_quant_e4m3(const croq_view2* src, const croq_view1* perm_t
       static_cast<const unsigned long long*>(peer_scale_ptrs->ptr), static_cast<int>(k),
       static_cast<int>(T), static_cast<int>(E), experts_per_rank, capacity_rows, static_cast<int>(H),
       st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* scale_src,
+                                  const croq_view1* perm_to_src, const croq_view2* topk_idx,
+                                  const croq_view1* expert_offsets, const croq_view1* dest_base,
+                                  const croq_view1* peer_q_ptrs, const croq_view1* peer_scale_ptrs,
+                                  int experts_per_rank, int capacity_rows, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(q_src) || !view_ok(scale_src) || !view_ok(perm_to_src) || !view_ok(topk_idx) ||
+      !view_ok(expert_offsets) || !view_ok(dest_base) || !view_ok(peer_q_ptrs) ||
+      !view_ok(peer_scale_ptrs))
+    return CROQ_ERR_NULL;
+  const size_t T = q_src->dims[0], H = q_src->dims[1], rows = perm_to_src->dims[0];
+  const size_t SB = scale_src->dims[1];
+  const size_t k = topk_idx->dims[1], E = dest_base->dims[0], W = peer_q_ptrs->dims[0];
+  if (topk_idx->dims[0] != T || k == 0 || rows != T * k) return CROQ_ERR_SHAPE;
+  if (scale_src->dims[0] != T || SB * 128 != H) return CROQ_ERR_SHAPE;
+  if (expert_offsets->dims[0] != E + 1 || peer_scale_ptrs->dims[0] != W) return CROQ_ERR_SHAPE;
+  if (experts_per_rank <= 0 || capacity_rows <= 0 || W * static_cast<size_t>(experts_per_rank) != E)
+    return CROQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (!aligned16(q_src->ptr) || (reinterpret_cast<uintptr_t>(scale_src->ptr) & 3u) != 0)
+    return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (rows == 0) return CROQ_OK;
+  constexpr int kRows = 4;
+  moe_dispatch_rows_q_kernel<kRows><<<static_cast<unsigned>((rows + kRows - 1) / kRows), kRowThreads,
+                                      0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint8_t*>(q_src->ptr), static_cast<const float*>(scale_src->ptr),
+      static_cast<const int*>(perm_to_src->ptr), static_cast<const int*>(topk_idx->ptr),
+      static_cast<const int*>(expert_offsets->ptr), static_cast<const int*>(dest_base->ptr),
+      static_cast<const unsigned long long*>(peer_q_ptrs->ptr),
+      static_cast<const unsigned long long*>(peer_scale_ptrs->ptr), static_cast<int>(k),
+      static_cast<int>(T), static_cast<int>(E), static_cast<int>(rows), experts_per_rank,
+      capacity_rows, static_cast<int>(H), static_cast<int>(SB), st->status_dev);
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

@@ -2,10 +2,11 @@
 // with the 1x128 e4m3 activation quantiser), the stand-alone row quantiser,
 // and the weighted combine back into token order.
 //
-// All four are HBM-bound: one CTA per destination row, 128-bit loads and
-// stores along the row, warp shuffles for the per-block amax. Algorithmic
-// bytes per row of H bf16 elements: permute 2H read + 2H written (+4 B index);
-// permute+quant 2H read + H + 4*H/128 written; combine k*2H read + 2H written.
+// All of them are HBM-bound: one CTA per destination row (or four), 128-bit
+// loads and stores along the row, warp shuffles for the per-block amax.
+// Algorithmic bytes per row of H bf16 elements: permute 2H read + 2H written
+// (+4 B index); permute+quant 2H read + H + 4*H/128 written; gather of
+// quantised rows H + 4*H/128 read and written; combine k*2H read + 2H written.
 // The reference has no counterpart for these kernels; the contract is stated
 // with the entry points in croq_b200.h.
 #include <cuda_bf16.h>
@@ -43,6 +44,60 @@ moe_permute_kernel(const uint16_t* __restrict__ src, const int* __restrict__ per
     for (int i = threadIdx.x; i < H / 8; i += kRowThreads) d4[i] = __ldg(s4 + i);
   } else {
     for (int i = threadIdx.x; i < H; i += kRowThreads) d[i] = s[i];
+  }
+}
+
+// Gather of rows that are already quantised: q_dst[pos,:] = q_src[perm_to_src[pos] / k, :]
+// and the same for the scale rows. Quantising the T token rows once and moving
+// e4m3 rows afterwards reads half the bytes of the fused gather + quantiser
+// (every token is gathered k times) and keeps the source (T x H bytes) small
+// enough to be served from L2. A CTA moves kRows rows and issues all its loads
+// before the first store. H % 16 == 0.
+template <int kRows>
+__global__ void __launch_bounds__(kRowThreads)
+moe_permute_q_kernel(const uint8_t* __restrict__ q_src, const float* __restrict__ s_src,
+                     const int* __restrict__ perm_to_src, int k, int T, int rows, int H, int SB,
+                     uint8_t* __restrict__ q_dst, float* __restrict__ s_dst,
+                     int* __restrict__ status) {
+  const int pos0 = blockIdx.x * kRows;
+  int src_row[kRows];
+  bool live[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int pos = pos0 + r;
+    live[r] = pos < rows;
+    src_row[r] = 0;
+    if (live[r]) {
+      const int idx = perm_to_src[pos];
+      const int t = idx / k;
+      if (idx < 0 || t >= T) {
+        if (threadIdx.x == 0) *status = kDevBadIndex;
+        live[r] = false;
+      } else {
+        src_row[r] = t;
+      }
+    }
+  }
+  const int chunks = H / 16;
+  for (int c = threadIdx.x; c < chunks; c += kRowThreads) {
+    uint4 v[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      v[r] = live[r] ? __ldg(reinterpret_cast<const uint4*>(q_src + static_cast<size_t>(src_row[r]) * H) + c)
+                     : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      if (live[r]) reinterpret_cast<uint4*>(q_dst + static_cast<size_t>(pos0 + r) * H)[c] = v[r];
+  }
+  for (int i = threadIdx.x; i < SB * kRows; i += kRowThreads) {
+    const int r = i / SB, j = i - r * SB;
+    // live[] is indexed with a run-time r: select through the unrolled loop
+    bool ok = false;
+    int t = 0;
+#pragma unroll
+    for (int q = 0; q < kRows; ++q)
+      if (q == r) { ok = live[q]; t = src_row[q]; }
+    if (ok) s_dst[static_cast<size_t>(pos0 + r) * SB + j] = __ldg(s_src + static_cast<size_t>(t) * SB + j);
   }
 }
 
@@ -245,6 +300,40 @@ int croq_moe_permute_quant_e4m3(const croq_view2* src, const croq_view1* perm_to
   croq::clear_error();
   if (perm_to_src == nullptr) return CROQ_ERR_NULL;
   return croq::launch_quant(src, perm_to_src, k, dst_q, dst_scale, stream);
+}
+
+int croq_moe_permute_q_e4m3(const croq_view2* q_src, const croq_view2* scale_src,
+                            const croq_view1* perm_to_src, int k, const croq_view2* q_dst,
+                            const croq_view2* scale_dst, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(q_src) || !view_ok(scale_src) || !view_ok(perm_to_src) || !view_ok(q_dst) ||
+      !view_ok(scale_dst))
+    return CROQ_ERR_NULL;
+  const size_t T = q_src->dims[0], H = q_src->dims[1], rows = perm_to_src->dims[0];
+  const size_t SB = scale_src->dims[1];
+  if (k <= 0) return CROQ_ERR_SHAPE;
+  if (scale_src->dims[0] != T || SB * 128 != H) return CROQ_ERR_SHAPE;
+  if (q_dst->dims[0] != rows || q_dst->dims[1] != H) return CROQ_ERR_SHAPE;
+  if (scale_dst->dims[0] != rows || scale_dst->dims[1] != SB) return CROQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFull || T > 0x7FFFFFFFull || H > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+  if (!aligned16(q_src->ptr) || !aligned16(q_dst->ptr) ||
+      (reinterpret_cast<uintptr_t>(scale_src->ptr) & 3u) != 0 ||
+      (reinterpret_cast<uintptr_t>(scale_dst->ptr) & 3u) != 0)
+    return CROQ_ERR_ALIGN;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (rows == 0 || H == 0) return CROQ_OK;
+  constexpr int kRows = 4;
+  moe_permute_q_kernel<kRows><<<static_cast<unsigned>((rows + kRows - 1) / kRows), kRowThreads, 0,
+                                static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint8_t*>(q_src->ptr), static_cast<const float*>(scale_src->ptr),
+      static_cast<const int*>(perm_to_src->ptr), k, static_cast<int>(T), static_cast<int>(rows),
+      static_cast<int>(H), static_cast<int>(SB), static_cast<uint8_t*>(q_dst->ptr),
+      static_cast<float*>(scale_dst->ptr), st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
 }
 
 int croq_quant_rows_e4m3(const croq_view2* x, const croq_view2* q, const croq_view2* scale,

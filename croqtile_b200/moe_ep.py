@@ -37,7 +37,8 @@ class CudaBackend:
         return self.api.moe_route_topk(logits, k)
 
     def permute_quant(self, x, perm_to_src, k):
-        return self.api.moe_permute_quant_e4m3(x, perm_to_src, k)
+        q, s = self.api.quant_rows_e4m3(x)      # once per token, then gather e4m3 rows
+        return self.api.moe_permute_q_e4m3(q, s, perm_to_src, k)
 
     def quant_rows(self, x):
         return self.api.quant_rows_e4m3(x)

@@ -122,10 +122,13 @@ class FusedExpertParallel:
         offsets[1:] = mine.cumsum(0, dtype=torch.int32)
         mark("counts+placement")
 
-        rc = lib.croq_moe_dispatch_quant_e4m3(_v2(x), _v1(r["perm_to_src"]), _v2(r["topk_idx"]),
-                                              _v1(r["expert_offsets"]), _v1(dest_base), _v1(self.peer_q),
-                                              _v1(self.peer_s), self.e_loc, self.capacity, stream)
-        _lib.check(rc, "croq_moe_dispatch_quant_e4m3")
+        # quantise the local tokens once, then send e4m3 rows (each token goes to k owners)
+        xq0, xs0 = api.quant_rows_e4m3(x)
+        rc = lib.croq_moe_dispatch_rows_q_e4m3(_v2(xq0), _v2(xs0), _v1(r["perm_to_src"]),
+                                               _v2(r["topk_idx"]), _v1(r["expert_offsets"]),
+                                               _v1(dest_base), _v1(self.peer_q), _v1(self.peer_s),
+                                               self.e_loc, self.capacity, stream)
+        _lib.check(rc, "croq_moe_dispatch_rows_q_e4m3")
         self._barrier()                      # all rows addressed to me have landed
         mark("dispatch")
 

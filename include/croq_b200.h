@@ -225,6 +225,14 @@ int croq_moe_permute_quant_e4m3(const croq_view2* src, const croq_view1* perm_to
                                 const croq_view2* dst_q, const croq_view2* dst_scale,
                                 croq_stream stream);
 
+/* The same result in two steps that move fewer bytes: quantise the T token rows
+ * once (croq_quant_rows_e4m3), then gather the quantised rows and their scales:
+ * q_dst[pos,:] = q_src[perm_to_src[pos] / k, :], scale_dst likewise.
+ * q_src e4m3 [T,H], scale_src f32 [T,H/128], q_dst [T*k,H], scale_dst [T*k,H/128]. */
+int croq_moe_permute_q_e4m3(const croq_view2* q_src, const croq_view2* scale_src,
+                            const croq_view1* perm_to_src, int k, const croq_view2* q_dst,
+                            const croq_view2* scale_dst, croq_stream stream);
+
 /* Weighted combine: out[t,:] = RN_bf16( sum_j topk_w[t,j] * y[src_to_perm[t*k+j], :] ),
  * summed in ascending j in fp32. y bf16 [T*k,H]; out bf16 [T,H]. */
 int croq_moe_unpermute(const croq_view2* y, const croq_view1* src_to_perm,
@@ -271,6 +279,16 @@ int croq_moe_dispatch_quant_e4m3(const croq_view2* src, const croq_view1* perm_t
                                  const croq_view1* dest_base, const croq_view1* peer_q_ptrs,
                                  const croq_view1* peer_scale_ptrs, int experts_per_rank,
                                  int capacity_rows, croq_stream stream);
+
+/* Dispatch of rows quantised once per token beforehand (croq_quant_rows_e4m3 on
+ * the local tokens): copies row perm_to_src[pos] / k of q_src e4m3 [T,H] and
+ * scale_src f32 [T,H/128] into the owner's buffers with 16-byte peer stores.
+ * Same placement and bit-identical buffers as croq_moe_dispatch_quant_e4m3. */
+int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* scale_src,
+                                  const croq_view1* perm_to_src, const croq_view2* topk_idx,
+                                  const croq_view1* expert_offsets, const croq_view1* dest_base,
+                                  const croq_view1* peer_q_ptrs, const croq_view1* peer_scale_ptrs,
+                                  int experts_per_rank, int capacity_rows, croq_stream stream);
 
 /* Combine: weighted unpermute (as croq_moe_unpermute) reading every expert
  * output row from the owner's y [capacity,H] bf16 buffer with peer loads. */

@@ -107,6 +107,11 @@ def test_quantisers_bit_exact(oracle):
     src_row = r["perm_to_src"] // k
     np.testing.assert_array_equal(bits_of(q2), rq[src_row])
     np.testing.assert_array_equal(s2.cpu().numpy().view(np.uint32), rs[src_row].view(np.uint32))
+    # quantise once, gather the quantised rows: the same bytes
+    q3, s3 = api.moe_permute_q_e4m3(q, s, to_dev(r["perm_to_src"]), k)
+    api.synchronize()
+    np.testing.assert_array_equal(bits_of(q3), rq[src_row])
+    np.testing.assert_array_equal(s3.cpu().numpy().view(np.uint32), rs[src_row].view(np.uint32))
 
 
 def test_bad_permutation_index_is_reported(oracle):
