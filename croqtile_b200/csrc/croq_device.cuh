@@ -499,10 +499,11 @@ __device__ __forceinline__ uint16_t pack1(float v) {
 // both the row-per-lane writes and the segment-per-8-lanes reads free of bank
 // conflicts. `stage` is this warp's area of 32*kChunks*16 bytes (16-byte
 // aligned); rows >= rows_valid are not stored. All 32 lanes must call.
-template <int kChunks>
-__device__ __forceinline__ void warp_store_rows(void* out_block, size_t ld_bytes, int rows_valid,
-                                                uint4* stage, const uint4 (&pk)[kChunks],
-                                                int lane) {
+// General form: row_ptr(r) gives the address at which row r's kChunks*16 bytes
+// start (only called for r < rows_valid), so rows may go to unrelated places.
+template <int kChunks, class RowPtr>
+__device__ __forceinline__ void warp_store_rows_to(RowPtr row_ptr, int rows_valid, uint4* stage,
+                                                   const uint4 (&pk)[kChunks], int lane) {
   static_assert(kChunks == 8 || kChunks == 4, "row segments of 128 or 64 bytes");
   constexpr int kRowsPerStore = 32 / kChunks;
   {
@@ -512,15 +513,28 @@ __device__ __forceinline__ void warp_store_rows(void* out_block, size_t ld_bytes
   }
   __syncwarp();
   const int c = lane % kChunks;
-  uint8_t* const out_bytes = static_cast<uint8_t*>(out_block) + c * 16;
 #pragma unroll
   for (int i = 0; i < kChunks; ++i) {
     const int r = i * kRowsPerStore + lane / kChunks;
     const int swz = (kChunks == 8) ? (r & 7) : ((r >> 1) & 3);
     const uint4 v = stage[r * kChunks + (c ^ swz)];
-    if (r < rows_valid) *reinterpret_cast<uint4*>(out_bytes + static_cast<size_t>(r) * ld_bytes) = v;
+    if (r < rows_valid) {
+      uint8_t* dst = row_ptr(r);
+      if (dst != nullptr) *reinterpret_cast<uint4*>(dst + c * 16) = v;
+    }
   }
   __syncwarp();
+}
+
+// Rows of one dense matrix: row r starts at out_block + r * ld_bytes.
+template <int kChunks>
+__device__ __forceinline__ void warp_store_rows(void* out_block, size_t ld_bytes, int rows_valid,
+                                                uint4* stage, const uint4 (&pk)[kChunks],
+                                                int lane) {
+  uint8_t* const base = static_cast<uint8_t*>(out_block);
+  warp_store_rows_to<kChunks>(
+      [base, ld_bytes](int r) { return base + static_cast<size_t>(r) * ld_bytes; }, rows_valid,
+      stage, pk, lane);
 }
 
 // Drains kCols fp32 accumulator columns of the calling warp's 32 TMEM lanes

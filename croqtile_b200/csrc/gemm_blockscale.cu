@@ -81,6 +81,13 @@ struct BlockScaleParams {
   int out_ld;            // output row pitch in elements
   const int* expert_offsets;  // grouped: [E+1] device array
   int E;
+  // Grouped mode with scattered output rows (expert-parallel combine fused into
+  // the epilogue): row r of the product goes to row (row_ret[r] & 0xffffffff) of
+  // the [peer_rows, N] buffer at peer_out[row_ret[r] >> 32], which may be another
+  // GPU's memory (plain 16-byte stores over NVLink). Null: rows go to `out`.
+  const long long* row_ret;
+  const unsigned long long* peer_out;
+  int world, peer_rows;
   int* status;
 };
 
@@ -417,7 +424,53 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       } else {
         const int col_base = t.n0 + half * 128;
         const int row0 = t.m0 + quarter * 32;
-        if (vec_ok && col_base + 128 <= p.N) {
+        if (kMode == kGrouped && p.row_ret != nullptr) {
+          // Scattered rows: the destination of row r is looked up by the lanes
+          // that store it. A return entry outside the peers' buffers is reported
+          // and skipped, never dereferenced.
+          const bool whole = vec_ok && col_base + 128 <= p.N;
+          auto dest_of = [&p, col_base](int row) -> uint8_t* {
+            const long long ret = __ldg(p.row_ret + row);
+            const int home = static_cast<int>(ret >> 32);
+            const long long rr = ret & 0xFFFFFFFFll;
+            if (home < 0 || home >= p.world || rr >= p.peer_rows) {
+              *p.status = kDevBadIndex;
+              return nullptr;
+            }
+            return reinterpret_cast<uint8_t*>(__ldg(p.peer_out + home)) +
+                   (static_cast<size_t>(rr) * p.N + col_base) * 2;
+          };
+          if (whole) {
+#pragma unroll
+            for (int b = 0; b < 16 / kChunks; ++b) {
+              uint4 pk[kChunks];
+#pragma unroll
+              for (int c = 0; c < kChunks; ++c) {
+                const int q = b * kChunks + c;
+                pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
+                pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
+                pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
+                pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+              }
+              warp_store_rows_to<kChunks>(
+                  [&dest_of, row0, b](int r) -> uint8_t* {
+                    uint8_t* d = dest_of(row0 + r);
+                    return d == nullptr ? nullptr : d + b * kChunks * 16;
+                  },
+                  t.m_end - row0, out_stage, pk, lane);
+            }
+          } else if (row < t.m_end && col_base < p.N) {
+            uint8_t* d = dest_of(row);
+            if (d != nullptr) {
+              uint16_t* out_row = reinterpret_cast<uint16_t*>(d);
+#pragma unroll
+              for (int i = 0; i < 64; ++i) {
+                if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+                if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
+              }
+            }
+          }
+        } else if (vec_ok && col_base + 128 <= p.N) {
           uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
 #pragma unroll
           for (int b = 0; b < 16 / kChunks; ++b) {
@@ -850,16 +903,21 @@ extern "C" int croq_blockscale_gemm_e4m3_ex(const croq_view2* lhs, const croq_vi
                                 scale_lhs_layout, stream);
 }
 
-extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
-                                          const croq_view3* w, const croq_view3* w_scale,
-                                          const croq_view1* expert_offsets,
-                                          const croq_view2* out, int swiglu,
-                                          croq_stream stream_) {
-  using namespace croq;
+namespace croq {
+namespace {
+
+// `out` == nullptr selects the scattered form: row_ret / peer_out_ptrs name the
+// destination of every row (see BlockScaleParams::row_ret).
+int grouped_entry(const croq_view2* x, const croq_view2* x_scale, const croq_view3* w,
+                  const croq_view3* w_scale, const croq_view1* expert_offsets,
+                  const croq_view2* out, int swiglu, const croq_view1* row_ret,
+                  const croq_view1* peer_out_ptrs, int peer_rows, croq_stream stream_) {
   clear_error();
+  const bool scatter = out == nullptr;
   if (!view_ok(x) || !view_ok(x_scale) || !view_ok(w) || !view_ok(w_scale) ||
-      !view_ok(expert_offsets) || !view_ok(out))
+      !view_ok(expert_offsets))
     return CROQ_ERR_NULL;
+  if (scatter ? (!view_ok(row_ret) || !view_ok(peer_out_ptrs)) : !view_ok(out)) return CROQ_ERR_NULL;
   const size_t R = x->dims[0], K = x->dims[1];
   const size_t E = w->dims[0], N = w->dims[1];
   if (w->dims[2] != K || E == 0 || N == 0) return CROQ_ERR_SHAPE;
@@ -871,11 +929,21 @@ extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2*
   if (w_scale->dims[0] != E || w_scale->dims[1] != NB || w_scale->dims[2] != KB) return CROQ_ERR_SHAPE;
   const size_t out_cols = swiglu ? N / 2 : N;
   if (swiglu && (N % 256 != 0)) return CROQ_ERR_UNSUPPORTED;  // gate/up halves of whole 128-blocks
-  if (out->dims[0] != R || out->dims[1] != out_cols) return CROQ_ERR_SHAPE;
+  if (scatter) {
+    if (swiglu) return CROQ_ERR_UNSUPPORTED;
+    if (row_ret->dims[0] < R || peer_out_ptrs->dims[0] == 0 || peer_rows <= 0) return CROQ_ERR_SHAPE;
+    if (peer_out_ptrs->dims[0] > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+    if (N % 8 != 0) return CROQ_ERR_ALIGN;   // 16-byte row segments at every destination
+    if ((reinterpret_cast<uintptr_t>(row_ret->ptr) & 7u) != 0 ||
+        (reinterpret_cast<uintptr_t>(peer_out_ptrs->ptr) & 7u) != 0)
+      return CROQ_ERR_ALIGN;
+  } else if (out->dims[0] != R || out->dims[1] != out_cols) {
+    return CROQ_ERR_SHAPE;
+  }
   if (K == 0 || K % 16 != 0) return K == 0 ? CROQ_ERR_UNSUPPORTED : CROQ_ERR_ALIGN;
   if ((N * K) % 16 != 0) return CROQ_ERR_ALIGN;
   if (!aligned16(x->ptr) || !aligned16(w->ptr)) return CROQ_ERR_ALIGN;
-  if ((reinterpret_cast<uintptr_t>(out->ptr) & 1u) != 0 ||
+  if ((!scatter && (reinterpret_cast<uintptr_t>(out->ptr) & 1u) != 0) ||
       (reinterpret_cast<uintptr_t>(x_scale->ptr) & 3u) != 0 ||
       (reinterpret_cast<uintptr_t>(w_scale->ptr) & 3u) != 0 ||
       (reinterpret_cast<uintptr_t>(expert_offsets->ptr) & 3u) != 0)
@@ -886,7 +954,13 @@ extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2*
   if (R == 0) return CROQ_OK;
 
   BlockScaleParams p = {};
-  p.out = static_cast<uint16_t*>(out->ptr);
+  p.out = scatter ? nullptr : static_cast<uint16_t*>(out->ptr);
+  if (scatter) {
+    p.row_ret = static_cast<const long long*>(row_ret->ptr);
+    p.peer_out = static_cast<const unsigned long long*>(peer_out_ptrs->ptr);
+    p.world = static_cast<int>(peer_out_ptrs->dims[0]);
+    p.peer_rows = peer_rows;
+  }
   p.scale_a = static_cast<const float*>(x_scale->ptr);
   p.sa_row = x_scale->dims[1];
   p.sa_kb = 1;
@@ -917,4 +991,30 @@ extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2*
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   return swiglu ? launch_kernel<true, kGroupedSwiGLU>(map_a, map_b, p, grid, stream)
                 : launch_kernel<true, kGrouped>(map_a, map_b, p, grid, stream);
+}
+
+}  // namespace
+}  // namespace croq
+
+extern "C" int croq_moe_grouped_gemm_e4m3(const croq_view2* x, const croq_view2* x_scale,
+                                          const croq_view3* w, const croq_view3* w_scale,
+                                          const croq_view1* expert_offsets,
+                                          const croq_view2* out, int swiglu,
+                                          croq_stream stream) {
+  if (out == nullptr) {
+    croq::clear_error();
+    return CROQ_ERR_NULL;
+  }
+  return croq::grouped_entry(x, x_scale, w, w_scale, expert_offsets, out, swiglu, nullptr, nullptr,
+                             0, stream);
+}
+
+extern "C" int croq_moe_grouped_gemm_e4m3_scatter(const croq_view2* x, const croq_view2* x_scale,
+                                                  const croq_view3* w, const croq_view3* w_scale,
+                                                  const croq_view1* expert_offsets,
+                                                  const croq_view1* row_ret,
+                                                  const croq_view1* peer_out_ptrs, int peer_rows,
+                                                  croq_stream stream) {
+  return croq::grouped_entry(x, x_scale, w, w_scale, expert_offsets, nullptr, 0, row_ret,
+                             peer_out_ptrs, peer_rows, stream);
 }

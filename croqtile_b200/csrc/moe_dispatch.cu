@@ -100,9 +100,10 @@ moe_dispatch_rows_q_kernel(const uint8_t* __restrict__ q_src, const float* __res
                            const int* __restrict__ perm_to_src, const int* __restrict__ topk_idx,
                            const int* __restrict__ expert_offsets, const int* __restrict__ dest_base,
                            const unsigned long long* __restrict__ peer_q,
-                           const unsigned long long* __restrict__ peer_scale, int k, int T, int E,
-                           int rows, int experts_per_rank, int capacity_rows, int H, int SB,
-                           int* __restrict__ status) {
+                           const unsigned long long* __restrict__ peer_scale,
+                           const unsigned long long* __restrict__ peer_ret, int my_rank, int k,
+                           int T, int E, int rows, int experts_per_rank, int capacity_rows, int H,
+                           int SB, int* __restrict__ status) {
   const int pos0 = blockIdx.x * kRows;
   const uint8_t* src_q[kRows];
   const float* src_s[kRows];
@@ -137,6 +138,11 @@ moe_dispatch_rows_q_kernel(const uint8_t* __restrict__ q_src, const float* __res
     src_s[j] = s_src + static_cast<size_t>(t) * SB;
     dst_q[j] = reinterpret_cast<uint8_t*>(peer_q[owner]) + static_cast<size_t>(dest_row) * H;
     dst_s[j] = reinterpret_cast<float*>(peer_scale[owner]) + static_cast<size_t>(dest_row) * SB;
+    // return address of the row: (home rank, expanded row index), read by the
+    // owner's down-projection when it sends the result row straight back
+    if (peer_ret != nullptr && threadIdx.x == 0)
+      reinterpret_cast<long long*>(peer_ret[owner])[dest_row] =
+          (static_cast<long long>(my_rank) << 32) | static_cast<long long>(r);
   }
   const int chunks = H / 16;
   for (int c = threadIdx.x; c < chunks; c += kRowThreads) {
@@ -261,6 +267,7 @@ int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* sca
                                   const croq_view1* perm_to_src, const croq_view2* topk_idx,
                                   const croq_view1* expert_offsets, const croq_view1* dest_base,
                                   const croq_view1* peer_q_ptrs, const croq_view1* peer_scale_ptrs,
+                                  const croq_view1* peer_ret_ptrs, int my_rank,
                                   int experts_per_rank, int capacity_rows, croq_stream stream_) {
   using namespace croq;
   clear_error();
@@ -268,6 +275,10 @@ int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* sca
       !view_ok(expert_offsets) || !view_ok(dest_base) || !view_ok(peer_q_ptrs) ||
       !view_ok(peer_scale_ptrs))
     return CROQ_ERR_NULL;
+  if (peer_ret_ptrs != nullptr &&
+      (!view_ok(peer_ret_ptrs) || peer_ret_ptrs->dims[0] != peer_q_ptrs->dims[0] || my_rank < 0 ||
+       static_cast<size_t>(my_rank) >= peer_q_ptrs->dims[0]))
+    return peer_ret_ptrs->ptr == nullptr ? CROQ_ERR_NULL : CROQ_ERR_SHAPE;
   const size_t T = q_src->dims[0], H = q_src->dims[1], rows = perm_to_src->dims[0];
   const size_t SB = scale_src->dims[1];
   const size_t k = topk_idx->dims[1], E = dest_base->dims[0], W = peer_q_ptrs->dims[0];
@@ -290,9 +301,10 @@ int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* sca
       static_cast<const int*>(perm_to_src->ptr), static_cast<const int*>(topk_idx->ptr),
       static_cast<const int*>(expert_offsets->ptr), static_cast<const int*>(dest_base->ptr),
       static_cast<const unsigned long long*>(peer_q_ptrs->ptr),
-      static_cast<const unsigned long long*>(peer_scale_ptrs->ptr), static_cast<int>(k),
-      static_cast<int>(T), static_cast<int>(E), static_cast<int>(rows), experts_per_rank,
-      capacity_rows, static_cast<int>(H), static_cast<int>(SB), st->status_dev);
+      static_cast<const unsigned long long*>(peer_scale_ptrs->ptr),
+      peer_ret_ptrs != nullptr ? static_cast<const unsigned long long*>(peer_ret_ptrs->ptr) : nullptr,
+      my_rank, static_cast<int>(k), static_cast<int>(T), static_cast<int>(E), static_cast<int>(rows),
+      experts_per_rank, capacity_rows, static_cast<int>(H), static_cast<int>(SB), st->status_dev);
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

@@ -26,7 +26,7 @@ namespace croq {
 namespace {
 
 constexpr int kTokensPerBlock = 64;
-constexpr int kWarpsPerBlock = 8;
+constexpr int kWarpsPerBlock = 16;   // four tokens per warp: the per-token chain is latency-bound
 constexpr int kMaxExperts = 1024;
 
 // Monotone map float -> uint32 with -0 folded into +0 and NaN below -inf, so

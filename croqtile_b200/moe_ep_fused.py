@@ -1,20 +1,24 @@
-"""Expert-parallel MoE layer with the token exchange fused into the row kernels.
+"""Expert-parallel MoE layer with the token exchange fused into the kernels.
 
 Same layer and same results as ``croqtile_b200.moe_ep.moe_forward_ep``, but no
-library all-to-all and no regroup pass: every rank keeps three receive buffers
-in symmetric (peer-mapped) memory and
+library all-to-all and no regroup pass: every rank keeps its receive buffers in
+symmetric (peer-mapped) memory and
 
-  * the dispatch kernel (gather + e4m3 quantiser) stores each row directly at
-    its final expert-sorted position in the owner's buffer over NVLink,
+  * the dispatch kernel copies each quantised row, its scales and its return
+    address directly to its final expert-sorted position in the owner's buffers
+    over NVLink (the local tokens are quantised once beforehand),
   * the expert GEMMs run on the owner's buffer in place (tile table from the
     device-side offsets, so no host synchronisation anywhere in the step),
-  * the combine kernel loads each expert output row from the owner's buffer.
+  * the down projection's epilogue stores every result row straight into the
+    home rank's ``y_home`` buffer at row t*k+j, so the transfer of the combine
+    overlaps the GEMM's main loop; what is left of the combine is a local
+    weighted sum over k consecutive rows.
 
 The only collectives left are an 8 KB all-gather of the per-expert counts and
-three stream-ordered barriers per step (after dispatch, before combine, after
-combine). One process per GPU, ``torch.distributed`` (NCCL) for the plumbing.
-The reference has no MoE and no multi-GPU code; this module defines the
-behaviour.
+two stream-ordered barriers per step (after dispatch, after the down
+projection). One process per GPU, ``torch.distributed`` (NCCL) for the plumbing;
+only plain loads and stores cross the link. The reference has no MoE and no
+multi-GPU code; this module defines the behaviour.
 """
 from __future__ import annotations
 
@@ -24,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, api
-from ._lib import View1, View2
+from ._lib import View1, View2, View3
 
 
 def _v1(t):
@@ -33,6 +37,10 @@ def _v1(t):
 
 def _v2(t):
     return ctypes.byref(View2(t.data_ptr(), (ctypes.c_size_t * 2)(t.shape[0], t.shape[1])))
+
+
+def _v3(t):
+    return ctypes.byref(View3(t.data_ptr(), (ctypes.c_size_t * 3)(*t.shape)))
 
 
 class FusedExpertParallel:
@@ -56,15 +64,21 @@ class FusedExpertParallel:
         self.capacity = int(tokens_per_rank * k * capacity_factor + 127) // 128 * 128
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
-        # symmetric buffers: e4m3 rows (as bytes), their scales, bf16 expert outputs
+        # symmetric buffers. Received on the expert owner: e4m3 rows (as bytes), their
+        # scales and each row's return address. Received on the token's home rank: the
+        # expert outputs, one row per (token, pick) in t*k+j order.
+        self.home_rows = tokens_per_rank * k
         self.q_buf = symm_mem.empty((self.capacity, hidden), dtype=torch.uint8, device=dev)
         self.s_buf = symm_mem.empty((self.capacity, hidden // 128), dtype=torch.float32, device=dev)
-        self.y_buf = symm_mem.empty((self.capacity, hidden), dtype=torch.bfloat16, device=dev)
+        self.ret_buf = symm_mem.empty((self.capacity,), dtype=torch.int64, device=dev)
+        self.y_home = symm_mem.empty((self.home_rows, hidden), dtype=torch.bfloat16, device=dev)
         name = self.group.group_name
-        self._handles = [symm_mem.rendezvous(b, name) for b in (self.q_buf, self.s_buf, self.y_buf)]
+        self._handles = [symm_mem.rendezvous(b, name)
+                         for b in (self.q_buf, self.s_buf, self.ret_buf, self.y_home)]
         ptrs = [torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=dev)
                 for h in self._handles]
-        self.peer_q, self.peer_s, self.peer_y = ptrs
+        self.peer_q, self.peer_s, self.peer_ret, self.peer_y = ptrs
+        self._identity = torch.arange(self.home_rows, dtype=torch.int32, device=dev)
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self._lib = _lib.load()
 
@@ -123,13 +137,19 @@ class FusedExpertParallel:
         mark("counts+placement")
 
         # quantise the local tokens once, then send e4m3 rows (each token goes to k owners)
+        # together with the address their result has to come back to
+        if x.shape[0] * k > self.home_rows:
+            raise ValueError("more tokens than the buffers were sized for")
         xq0, xs0 = api.quant_rows_e4m3(x)
         rc = lib.croq_moe_dispatch_rows_q_e4m3(_v2(xq0), _v2(xs0), _v1(r["perm_to_src"]),
                                                _v2(r["topk_idx"]), _v1(r["expert_offsets"]),
                                                _v1(dest_base), _v1(self.peer_q), _v1(self.peer_s),
+                                               _v1(self.peer_ret), self.rank,
                                                self.e_loc, self.capacity, stream)
         _lib.check(rc, "croq_moe_dispatch_rows_q_e4m3")
-        self._barrier()                      # all rows addressed to me have landed
+        # All rows addressed to me have landed. It also orders this step after every
+        # rank's combine of the previous step, so peers may overwrite y_home again.
+        self._barrier()
         mark("dispatch")
 
         xq = self.q_buf.view(torch.float8_e4m3fn)
@@ -138,15 +158,17 @@ class FusedExpertParallel:
         gs = torch.empty((self.capacity, self.I // 128), dtype=torch.float32, device=self.dev)
         rc = lib.croq_quant_rows_e4m3_n(_v2(g), _v2(gq), _v2(gs), _v1(offsets[self.e_loc:]), stream)
         _lib.check(rc, "croq_quant_rows_e4m3_n")
-        api.moe_grouped_gemm_e4m3(gq, gs, w2, w2_scale, offsets, swiglu=False, out=self.y_buf)
-        self._barrier()                      # every owner's outputs are complete
+        # down projection; its epilogue stores every result row at its return address in
+        # the home rank's y_home (over NVLink, while the next tiles' main loops run)
+        rc = lib.croq_moe_grouped_gemm_e4m3_scatter(_v2(gq), _v2(gs), _v3(w2), _v3(w2_scale), _v1(offsets),
+                                                    _v1(self.ret_buf), _v1(self.peer_y), self.home_rows,
+                                                    stream)
+        _lib.check(rc, "croq_moe_grouped_gemm_e4m3_scatter")
+        self._barrier()                      # every owner has delivered my rows
         mark("expert_gemms")
 
-        out = torch.empty((x.shape[0], self.H), dtype=torch.bfloat16, device=self.dev)
-        rc = lib.croq_moe_combine_remote(_v1(self.peer_y), _v2(r["topk_idx"]), _v1(r["src_to_perm"]),
-                                         _v1(r["expert_offsets"]), _v1(dest_base), _v2(r["topk_w"]),
-                                         _v2(out), self.e_loc, self.capacity, stream)
-        _lib.check(rc, "croq_moe_combine_remote")
-        self._barrier()                      # peers are done reading my buffers: next step may overwrite
+        # rows of token t sit at y_home[t*k .. t*k+k-1]: a local weighted sum in ascending j
+        rows = x.shape[0] * k
+        out = api.moe_unpermute(self.y_home[:rows], self._identity[:rows], r["topk_w"])
         mark("combine")
         return out

@@ -283,12 +283,33 @@ int croq_moe_dispatch_quant_e4m3(const croq_view2* src, const croq_view1* perm_t
 /* Dispatch of rows quantised once per token beforehand (croq_quant_rows_e4m3 on
  * the local tokens): copies row perm_to_src[pos] / k of q_src e4m3 [T,H] and
  * scale_src f32 [T,H/128] into the owner's buffers with 16-byte peer stores.
- * Same placement and bit-identical buffers as croq_moe_dispatch_quant_e4m3. */
+ * Same placement and bit-identical buffers as croq_moe_dispatch_quant_e4m3.
+ * peer_ret_ptrs (may be NULL): u64 [world] bases of s64 [capacity] buffers; the
+ * owner's entry for each row receives (my_rank << 32) | (t*k+j), the address
+ * croq_moe_grouped_gemm_e4m3_scatter sends the result row back to. */
 int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* scale_src,
                                   const croq_view1* perm_to_src, const croq_view2* topk_idx,
                                   const croq_view1* expert_offsets, const croq_view1* dest_base,
                                   const croq_view1* peer_q_ptrs, const croq_view1* peer_scale_ptrs,
+                                  const croq_view1* peer_ret_ptrs, int my_rank,
                                   int experts_per_rank, int capacity_rows, croq_stream stream);
+
+/* Grouped GEMM (no SwiGLU) whose output rows are scattered instead of stored to
+ * one matrix: the expert-parallel combine's transfer fused into the epilogue.
+ * row_ret s64 [>= R]: for input row r, (home << 32) | row — as written by
+ * croq_moe_dispatch_rows_q_e4m3 into peer_ret_ptrs (u64 [world], buffers of
+ * s64 [capacity]) with home = the dispatching rank and row = the expanded row
+ * index t*k+j there. The product's row r goes to row `row` of the bf16
+ * [peer_rows, N] buffer at peer_out_ptrs[home] (u64 [world]; 16-byte aligned;
+ * other GPUs' buffers are written with plain 16-byte stores over NVLink, while
+ * the main loop of the next tiles runs). An entry outside [0,world) x
+ * [0,peer_rows) sets CROQ_ERR_INDEX and is skipped. N % 8 == 0. */
+int croq_moe_grouped_gemm_e4m3_scatter(const croq_view2* x, const croq_view2* x_scale,
+                                       const croq_view3* w, const croq_view3* w_scale,
+                                       const croq_view1* expert_offsets,
+                                       const croq_view1* row_ret,
+                                       const croq_view1* peer_out_ptrs, int peer_rows,
+                                       croq_stream stream);
 
 /* Combine: weighted unpermute (as croq_moe_unpermute) reading every expert
  * output row from the owner's y [capacity,H] bf16 buffer with peer loads. */

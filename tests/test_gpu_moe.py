@@ -184,3 +184,117 @@ def test_moe_forward_small_model_against_oracle(oracle):
     # requantisation of g can flip an e4m3 code where GPU and CPU differ by one
     # bf16 ulp, so the bound is the FP8 one with an absolute floor of 1e-2
     assert max_rel_err(got, ref, floor=1e-2 * max(1.0, np.abs(ref).max())) <= 2e-2
+
+
+def test_exchange_kernels_with_two_virtual_ranks_reproduce_the_layer():
+    """The expert-parallel exchange kernels on one GPU: two virtual ranks (each with its own
+    tokens, experts and receive buffers, launched one after the other) run dispatch ->
+    expert GEMMs -> results pushed back from the down projection's epilogue -> local
+    weighted sum. Every rank's output must equal the single-rank layer's rows bit for bit.
+    The earlier forms (gather + quantiser dispatch, combine by peer loads) must produce the
+    same buffers and the same output."""
+    import ctypes
+    from croqtile_b200 import _lib
+    from croqtile_b200.moe_ep_fused import _v1, _v2, _v3
+    lib = _lib.load()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(99)
+    T, H, I, E, k, W = 512, 512, 256, 8, 2, 2
+    x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn((T, E), generator=g, device=dev)
+
+    def quant(w):
+        e, n, kk = w.shape
+        blk = w.view(e, n // 128, 128, kk // 128, 128)
+        amax = blk.abs().amax((2, 4))
+        s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+        return (blk / s[:, :, None, :, None]).view(e, n, kk).to(torch.float8_e4m3fn), s.contiguous()
+
+    w13, w13s = quant(torch.randn((E, 2 * I, H), generator=g, device=dev) / H ** 0.5)
+    w2, w2s = quant(torch.randn((E, H, I), generator=g, device=dev) / I ** 0.5)
+    full = api.moe_forward(x, logits, w13, w13s, w2, w2s, k)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    t_loc, e_loc = T // W, E // W
+    cap, home_rows = T * k, t_loc * k
+    xs = [x[r * t_loc:(r + 1) * t_loc].contiguous() for r in range(W)]
+    routes = [api.moe_route_topk(logits[r * t_loc:(r + 1) * t_loc].contiguous(), k) for r in range(W)]
+    counts = torch.stack([rt["expert_counts"] for rt in routes])                # [W, E]
+    total = counts.sum(0, dtype=torch.int32)
+    per_owner = total.view(W, e_loc)
+    expert_start = (per_owner.cumsum(1, dtype=torch.int32) - per_owner).reshape(-1)
+
+    def table(bufs):
+        return torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+
+    q = [torch.zeros((cap, H), dtype=torch.uint8, device=dev) for _ in range(W)]
+    s = [torch.zeros((cap, H // 128), dtype=torch.float32, device=dev) for _ in range(W)]
+    q_old = [torch.zeros_like(b) for b in q]
+    s_old = [torch.zeros_like(b) for b in s]
+    ret = [torch.full((cap,), -1, dtype=torch.int64, device=dev) for _ in range(W)]
+    y_home = [torch.full((home_rows, H), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    y_own = [torch.zeros((cap, H), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    # pointer tables live as long as the kernels that read them (a temporary would hand its
+    # block back to the allocator before the launch)
+    t_q, t_s, t_q_old, t_s_old = table(q), table(s), table(q_old), table(s_old)
+    t_ret, t_y_home, t_y_own = table(ret), table(y_home), table(y_own)
+    bases = []
+    for r in range(W):                                                          # dispatch, both forms
+        rt = routes[r]
+        base = (expert_start + counts[:r].sum(0, dtype=torch.int32)).contiguous()
+        bases.append(base)
+        xq0, xs0 = api.quant_rows_e4m3(xs[r])
+        _lib.check(lib.croq_moe_dispatch_rows_q_e4m3(
+            _v2(xq0), _v2(xs0), _v1(rt["perm_to_src"]), _v2(rt["topk_idx"]), _v1(rt["expert_offsets"]),
+            _v1(base), _v1(t_q), _v1(t_s), _v1(t_ret), r, e_loc, cap, stream), "dispatch_rows_q")
+        _lib.check(lib.croq_moe_dispatch_quant_e4m3(
+            _v2(xs[r]), _v1(rt["perm_to_src"]), _v2(rt["topk_idx"]), _v1(rt["expert_offsets"]), _v1(base),
+            _v1(t_q_old), _v1(t_s_old), e_loc, cap, stream), "dispatch_quant")
+    api.synchronize()
+    for r in range(W):
+        assert torch.equal(q[r], q_old[r]) and torch.equal(s[r], s_old[r])
+    gqs = []
+    for r in range(W):                                                          # expert GEMMs of owner r
+        mine = total[r * e_loc:(r + 1) * e_loc]
+        offsets = torch.zeros(e_loc + 1, dtype=torch.int32, device=dev)
+        offsets[1:] = mine.cumsum(0, dtype=torch.int32)
+        n_rows = int(offsets[-1])
+        assert (ret[r][:n_rows] >= 0).all() and (ret[r][n_rows:] == -1).all()
+        ex = slice(r * e_loc, (r + 1) * e_loc)
+        act = api.moe_grouped_gemm_e4m3(q[r].view(torch.float8_e4m3fn), s[r], w13[ex].contiguous(),
+                                        w13s[ex].contiguous(), offsets, swiglu=True)
+        gq, gs = api.quant_rows_e4m3(act)
+        gqs.append((gq, gs, offsets, ex))
+        _lib.check(lib.croq_moe_grouped_gemm_e4m3_scatter(
+            _v2(gq), _v2(gs), _v3(w2[ex].contiguous()), _v3(w2s[ex].contiguous()), _v1(offsets),
+            _v1(ret[r]), _v1(t_y_home), home_rows, stream), "grouped_gemm_scatter")
+        api.moe_grouped_gemm_e4m3(gq, gs, w2[ex].contiguous(), w2s[ex].contiguous(), offsets, out=y_own[r])
+    api.synchronize()
+    identity = torch.arange(home_rows, dtype=torch.int32, device=dev)
+    for r in range(W):                                                          # combine, both forms
+        rt = routes[r]
+        want = full[r * t_loc:(r + 1) * t_loc]
+        got = api.moe_unpermute(y_home[r], identity, rt["topk_w"])
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"pushed rows, rank {r}"
+        old = torch.empty_like(got)
+        _lib.check(lib.croq_moe_combine_remote(
+            _v1(t_y_own), _v2(rt["topk_idx"]), _v1(rt["src_to_perm"]), _v1(rt["expert_offsets"]),
+            _v1(bases[r]), _v2(rt["topk_w"]), _v2(old), e_loc, cap, stream), "combine_remote")
+        api.synchronize()
+        assert torch.equal(old.view(torch.int16), want.view(torch.int16)), f"peer loads, rank {r}"
+
+    # a return address outside the peers' buffers is reported and never dereferenced
+    gq, gs, offsets, ex = gqs[0]
+    bad = ret[0].clone()
+    bad[3] = (5 << 32) | 1                       # rank 5 of 2
+    bad[4] = (1 << 32) | (home_rows + 7)         # row beyond the home buffer
+    before = [b.clone() for b in y_home]
+    _lib.check(lib.croq_moe_grouped_gemm_e4m3_scatter(
+        _v2(gq), _v2(gs), _v3(w2[ex].contiguous()), _v3(w2s[ex].contiguous()), _v1(offsets), _v1(bad),
+        _v1(t_y_home), home_rows, stream), "grouped_gemm_scatter")
+    with pytest.raises(CroqError) as err:
+        api.synchronize()
+    assert err.value.name == "CROQ_ERR_INDEX"
+    api.synchronize()
+    for a, b in zip(before, y_home):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))    # same rows rewritten, nothing else
