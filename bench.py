@@ -565,9 +565,9 @@ def run_moe_arm(args, T, H, I):
     lg = [torch.randn((t_loc, E), generator=g, device=dev) for _ in range(2)]
 
     fused = None
-    if world > 1 and args.ep == "fused":
+    if world > 1 and args.ep in ("fused", "fused-pull"):
         from croqtile_b200.moe_ep_fused import FusedExpertParallel
-        fused = FusedExpertParallel(H, I, E, t_loc, k)
+        fused = FusedExpertParallel(H, I, E, t_loc, k, push_results=(args.ep == "fused"))
 
     def layer(x_in, l_in, timers=None):
         if fused is not None:
@@ -691,7 +691,9 @@ def run_moe_arm(args, T, H, I):
             "config": {"workload": args.workload, "tokens_global": T, "hidden": H, "expert_intermediate": I,
                        "experts": E, "top_k": k, "experts_per_gpu": e_loc, "tokens_per_gpu": t_loc,
                        "parallelism": (f"ep{world}: tokens data-parallel, experts owner-partitioned, " +
-                                       ("dispatch/combine fused into the row kernels over NVLink peer memory"
+                                       (("dispatch by peer stores, results pushed back by the down projection's "
+                                         "epilogue over NVLink peer memory" if args.ep == "fused" else
+                                         "dispatch by peer stores, combine by peer loads over NVLink peer memory")
                                         if fused is not None else "NCCL all-to-all dispatch/combine"))
                        if world > 1 else "single GPU",
                        "l2": "expert weights (11.3 GB / world) stream from HBM every step; two token sets alternate"},
@@ -737,8 +739,9 @@ def main():
     ap.add_argument("--impl", default="croq", choices=["croq", "reference"])
     ap.add_argument("--workload", default="fp8_blockscale_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
-                    help="MoE workload at N > 1: exchange fused into the row kernels, or NCCL all-to-all")
+    ap.add_argument("--ep", default="fused", choices=["fused", "fused-pull", "nccl"],
+                    help="MoE workload at N > 1: exchange fused into the kernels (results pushed back by "
+                         "the down projection's epilogue, or pulled by the combine kernel), or NCCL all-to-all")
     args = ap.parse_args()
     kind, M, N, K = WORKLOADS[args.workload]
     if kind == "moe":

@@ -41,7 +41,6 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // one scale block; 128 x 1 B = one swizzle row
-constexpr int kStages = 4;
 constexpr int kThreads = 384;        // 4 control warps + 8 promotion warps
 constexpr int kEpiWarps = 8;
 // Register hand-off between warpgroups (setmaxnreg). A CTA can only re-assign
@@ -57,12 +56,21 @@ constexpr int kTmemCols = 512;
 constexpr uint32_t kABytes = kBlockM * kBlockK;
 constexpr uint32_t kBBytes = kBlockN * kBlockK;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-// Output staging for the coalesced store: each promotion warp owns 32 rows of
-// 128-byte (dense) or 64-byte (grouped: the tile tables need the room) segments.
-__host__ __device__ constexpr int epi_chunks(int mode) { return mode == 0 ? 8 : 4; }
+// Output path of the single-CTA kernel. Dense and plain grouped mode: a whole
+// 128x256 tile of 16-bit results is staged (each promotion warp owns 32 rows x
+// 128 columns = two 4 KB blocks of 128-byte, XOR-swizzled row segments) and a
+// dedicated store warp writes it out while the promotion warps already work on
+// the next tile, so neither HBM nor NVLink store latency sits on the tile's
+// critical path; three operand stages leave the room. SwiGLU mode (K is long,
+// the output tile small) keeps four operand stages, and its promotion warps
+// store their own rows through a 2 KB staging block each.
+constexpr uint32_t kOutWarpBytes = 32 * 256;
+constexpr uint32_t kOutStageBytes = kEpiWarps * kOutWarpBytes;   // 64 KB
+__host__ __device__ constexpr bool uses_store_warp(int mode) { return mode != 2; }
+__host__ __device__ constexpr int stages_of(int mode) { return uses_store_warp(mode) ? 3 : 4; }
 constexpr size_t smem_bytes(int mode) {
-  return static_cast<size_t>(kStages) * kStageBytes + 1024 +
-         static_cast<size_t>(kEpiWarps) * 32 * epi_chunks(mode) * 16;
+  return static_cast<size_t>(stages_of(mode)) * kStageBytes + 1024 +
+         (uses_store_warp(mode) ? kOutStageBytes : kEpiWarps * 32 * 64);
 }
 constexpr int kGroupM = 16;  // M tiles per rasterisation group
 
@@ -146,6 +154,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, const BlockScaleParams p) {
   extern __shared__ uint8_t smem_raw[];
+  constexpr int kStages = stages_of(kMode);
+  constexpr bool kStoreWarp = uses_store_warp(kMode);
   __shared__ int tile_prefix[(kMode == kDense) ? 1 : kMaxExperts + 1];
   __shared__ int offsets_s[(kMode == kDense) ? 1 : kMaxExperts + 1];
   // output columns one tile covers: SwiGLU pairs 128 gate with 128 up columns
@@ -156,12 +166,17 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            // partial is complete
   __shared__ __align__(8) uint64_t bar_part_empty[2];      // a TMEM partial buffer was drained
   __shared__ __align__(8) uint64_t bar_drain[2];
+  __shared__ __align__(8) uint64_t bar_out_full;    // all promotion warps left their results
+  __shared__ __align__(8) uint64_t bar_out_empty;   // the store warp has read the staging area
+  __shared__ int out_staged[kEpiWarps];             // 1: the warp's block is in the staging area
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint4* const out_stage_all = reinterpret_cast<uint4*>(
+      smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes);
   const int num_kb = p.KB;
   int total_work = p.total_work;
   if constexpr (kMode != kDense) {
@@ -207,6 +222,8 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&bar_part_empty[b]), kEpiWarps);  // one arrival per promotion warp
       mbar_init(smem_u32(&bar_drain[b]), 1);
     }
+    mbar_init(smem_u32(&bar_out_full), kEpiWarps);
+    mbar_init(smem_u32(&bar_out_empty), 1);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -305,6 +322,62 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       if (elect_one()) umma_commit(smem_u32(&bar_drain[buf]));
       __syncwarp();
       mbar_wait(smem_u32(&bar_drain[buf]), 0, abort_ptr);
+    } else if constexpr (kStoreWarp) {
+      // -------------------------------------------------------- store warp --
+      // Writes each finished tile from the staging area to its destination with
+      // 16-byte stores, eight lanes per 128-byte row segment: rows of `out`, or,
+      // in the scattered form, the row the return table names in a peer's buffer.
+      constexpr int kBlocks = 2;       // 64-column blocks per promotion warp
+      const int out_cols = p.out_ld;
+      uint32_t out_phase = 0;
+      const int c = lane & 7;
+      for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+        Tile t;
+        if constexpr (kMode == kDense) t = decode_dense(p, w);
+        else t = decode_grouped(p, tile_prefix, offsets_s, w, kTileCols);
+        if (!mbar_wait(smem_u32(&bar_out_full), out_phase, abort_ptr)) break;
+        for (int ew = 0; ew < kEpiWarps; ++ew) {
+          if (out_staged[ew] == 0) continue;
+          const int row0 = t.m0 + (ew & 3) * 32;
+          const int rows_valid = t.m_end - row0;
+          const int col_base = t.n0 + (ew >> 2) * (kBlocks * 64);
+          const uint4* region = out_stage_all + ew * (kOutWarpBytes / 16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            uint4 v[kBlocks];
+#pragma unroll
+            for (int b = 0; b < kBlocks; ++b) v[b] = region[(b * 32 + r) * 8 + (c ^ (r & 7))];
+            if (r < rows_valid) {
+              uint8_t* dst;
+              if (kMode == kGrouped && p.row_ret != nullptr) {
+                // a return entry outside the peers' buffers is reported, never dereferenced
+                const long long ret = __ldg(p.row_ret + row0 + r);
+                const int home = static_cast<int>(ret >> 32);
+                const long long rr = ret & 0xFFFFFFFFll;
+                if (home < 0 || home >= p.world || rr >= p.peer_rows) {
+                  *p.status = kDevBadIndex;
+                  dst = nullptr;
+                } else {
+                  dst = reinterpret_cast<uint8_t*>(__ldg(p.peer_out + home)) +
+                        (static_cast<size_t>(rr) * p.N + col_base) * 2;
+                }
+              } else {
+                dst = reinterpret_cast<uint8_t*>(p.out) +
+                      (static_cast<size_t>(row0 + r) * out_cols + col_base) * 2;
+              }
+              if (dst != nullptr) {
+#pragma unroll
+                for (int b = 0; b < kBlocks; ++b)
+                  *reinterpret_cast<uint4*>(dst + b * 128 + c * 16) = v[b];
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_out_empty));
+        out_phase ^= 1u;
+      }
     }
   } else {
     // ------------------------------------------------- promotion + store --
@@ -316,10 +389,9 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
     const int half = (warp - 4) >> 2;
     const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    constexpr int kChunks = epi_chunks(kMode);
-    uint4* const out_stage = reinterpret_cast<uint4*>(
-        smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kStageBytes) +
-        (warp - 4) * 32 * kChunks;
+    uint4* const region = out_stage_all + (warp - 4) * (kStoreWarp ? kOutWarpBytes / 16 : 128);
+    const int swz = lane & 7;
+    uint32_t out_phase = 0;
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -378,37 +450,17 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       if (!ok) break;
       if constexpr (kMode == kGroupedSwiGLU) {
-        // out[row, n0 + half*64 + c] = silu(gate_c) * up_c, c = 0..63
+        // out[row, n0 + half*64 + c] = silu(gate_c) * up_c, c = 0..63; this warp stores its
+        // own 32 rows, two 32-column blocks through its staging block
         const int col_base = t.n0 + half * 64;
         const int row0 = t.m0 + quarter * 32;
-        if (vec_ok && col_base + 64 <= (p.N >> 1)) {
-          // whole 64-column block: staged, coalesced store
-          uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+        const bool whole = vec_ok && col_base + 64 <= (p.N >> 1);
 #pragma unroll
-          for (int b = 0; b < 8 / kChunks; ++b) {
-            uint4 pk[kChunks];
+        for (int b = 0; b < 2; ++b) {
+          uint4 pk[4];
 #pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-              const int q = b * kChunks + c;
-              float r[8];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 g = acc[q * 4 + j], u = acc[32 + q * 4 + j];
-                r[2 * j] = (g.x / (1.0f + expf(-g.x))) * u.x;
-                r[2 * j + 1] = (g.y / (1.0f + expf(-g.y))) * u.y;
-              }
-              pk[c].x = pack2<kBf16>(r[0], r[1]);
-              pk[c].y = pack2<kBf16>(r[2], r[3]);
-              pk[c].z = pack2<kBf16>(r[4], r[5]);
-              pk[c].w = pack2<kBf16>(r[6], r[7]);
-            }
-            warp_store_rows<kChunks>(out_block + b * kChunks * 8, static_cast<size_t>(p.out_ld) * 2,
-                                     t.m_end - row0, out_stage, pk, lane);
-          }
-        } else if (row < t.m_end && col_base < (p.N >> 1)) {
-          uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
+          for (int c = 0; c < 4; ++c) {
+            const int q = b * 4 + c;
             float r[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -416,84 +468,65 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
               r[2 * j] = (g.x / (1.0f + expf(-g.x))) * u.x;
               r[2 * j + 1] = (g.y / (1.0f + expf(-g.y))) * u.y;
             }
+            pk[c] = make_uint4(pack2<kBf16>(r[0], r[1]), pack2<kBf16>(r[2], r[3]),
+                               pack2<kBf16>(r[4], r[5]), pack2<kBf16>(r[6], r[7]));
+            if (!whole && row < t.m_end && col_base < (p.N >> 1)) {
+              uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (col_base + q * 8 + j < (p.N >> 1)) out_row[q * 8 + j] = pack1<kBf16>(r[j]);
+              for (int j = 0; j < 8; ++j)
+                if (col_base + q * 8 + j < (p.N >> 1)) out_row[q * 8 + j] = pack1<kBf16>(r[j]);
+            }
           }
+          if (whole)
+            warp_store_rows<4>(p.out + static_cast<size_t>(row0) * p.out_ld + col_base + b * 32,
+                               static_cast<size_t>(p.out_ld) * 2, t.m_end - row0, region, pk, lane);
         }
-      } else {
+        continue;
+      }
+      // ---- results: into the staging area (the store warp writes them out), or, for a
+      // ragged / unaligned block, straight to memory one row per lane
+      ok = mbar_wait(smem_u32(&bar_out_empty), out_phase ^ 1u, abort_ptr);   // previous tile drained
+      if (!ok) break;
+      out_phase ^= 1u;
+      bool staged;
+      {
         const int col_base = t.n0 + half * 128;
-        const int row0 = t.m0 + quarter * 32;
-        if (kMode == kGrouped && p.row_ret != nullptr) {
-          // Scattered rows: the destination of row r is looked up by the lanes
-          // that store it. A return entry outside the peers' buffers is reported
-          // and skipped, never dereferenced.
-          const bool whole = vec_ok && col_base + 128 <= p.N;
-          auto dest_of = [&p, col_base](int row) -> uint8_t* {
+        staged = vec_ok && col_base + 128 <= p.N;
+        if (staged) {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            // 64-column block q / 8, 16-byte piece q % 8 of this lane's row
+            region[((q >> 3) * 32 + lane) * 8 + ((q & 7) ^ swz)] =
+                make_uint4(pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y),
+                           pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y),
+                           pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y),
+                           pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y));
+          }
+        } else if (row < t.m_end && col_base < p.N) {
+          uint16_t* out_row = nullptr;
+          if (kMode == kGrouped && p.row_ret != nullptr) {
             const long long ret = __ldg(p.row_ret + row);
             const int home = static_cast<int>(ret >> 32);
             const long long rr = ret & 0xFFFFFFFFll;
-            if (home < 0 || home >= p.world || rr >= p.peer_rows) {
-              *p.status = kDevBadIndex;
-              return nullptr;
-            }
-            return reinterpret_cast<uint8_t*>(__ldg(p.peer_out + home)) +
-                   (static_cast<size_t>(rr) * p.N + col_base) * 2;
-          };
-          if (whole) {
-#pragma unroll
-            for (int b = 0; b < 16 / kChunks; ++b) {
-              uint4 pk[kChunks];
-#pragma unroll
-              for (int c = 0; c < kChunks; ++c) {
-                const int q = b * kChunks + c;
-                pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-                pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-                pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-                pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
-              }
-              warp_store_rows_to<kChunks>(
-                  [&dest_of, row0, b](int r) -> uint8_t* {
-                    uint8_t* d = dest_of(row0 + r);
-                    return d == nullptr ? nullptr : d + b * kChunks * 16;
-                  },
-                  t.m_end - row0, out_stage, pk, lane);
-            }
-          } else if (row < t.m_end && col_base < p.N) {
-            uint8_t* d = dest_of(row);
-            if (d != nullptr) {
-              uint16_t* out_row = reinterpret_cast<uint16_t*>(d);
-#pragma unroll
-              for (int i = 0; i < 64; ++i) {
-                if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
-                if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
-              }
-            }
+            if (home < 0 || home >= p.world || rr >= p.peer_rows) *p.status = kDevBadIndex;
+            else out_row = reinterpret_cast<uint16_t*>(__ldg(p.peer_out + home)) +
+                           static_cast<size_t>(rr) * p.N + col_base;
+          } else {
+            out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
           }
-        } else if (vec_ok && col_base + 128 <= p.N) {
-          uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+          if (out_row != nullptr) {
 #pragma unroll
-          for (int b = 0; b < 16 / kChunks; ++b) {
-            uint4 pk[kChunks];
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-              const int q = b * kChunks + c;
-              pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-              pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-              pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-              pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
+            for (int i = 0; i < 64; ++i) {
+              if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
+              if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
             }
-            warp_store_rows<kChunks>(out_block + b * kChunks * 8, static_cast<size_t>(p.out_ld) * 2,
-                                     t.m_end - row0, out_stage, pk, lane);
-          }
-        } else if (row < t.m_end && col_base < p.N) {
-          uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
-            if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
           }
         }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        out_staged[warp - 4] = staged ? 1 : 0;
+        mbar_arrive(smem_u32(&bar_out_full));   // release: the staged block and the flag are visible
       }
     }
   }

@@ -49,10 +49,15 @@ class FusedExpertParallel:
     capacity_rows: rows each receive buffer can hold. The expected load is
     ``tokens_per_rank * k`` rows; routing imbalance needs head-room (default 2x).
     A row that does not fit is reported as CROQ_ERR_INDEX by ``api.synchronize``.
+
+    push_results: True (default) lets the down projection's epilogue store each result
+    row into the home rank's buffer; False keeps the results on the owner and lets the
+    combine kernel load them over NVLink (one more buffer and one more barrier per step).
+    Both give the same bits.
     """
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, tokens_per_rank: int, k: int,
-                 group=None, capacity_factor: float = 2.0):
+                 group=None, capacity_factor: float = 2.0, push_results: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -71,7 +76,9 @@ class FusedExpertParallel:
         self.q_buf = symm_mem.empty((self.capacity, hidden), dtype=torch.uint8, device=dev)
         self.s_buf = symm_mem.empty((self.capacity, hidden // 128), dtype=torch.float32, device=dev)
         self.ret_buf = symm_mem.empty((self.capacity,), dtype=torch.int64, device=dev)
-        self.y_home = symm_mem.empty((self.home_rows, hidden), dtype=torch.bfloat16, device=dev)
+        self.push_results = push_results
+        y_rows = self.home_rows if push_results else self.capacity
+        self.y_home = symm_mem.empty((y_rows, hidden), dtype=torch.bfloat16, device=dev)
         name = self.group.group_name
         self._handles = [symm_mem.rendezvous(b, name)
                          for b in (self.q_buf, self.s_buf, self.ret_buf, self.y_home)]
@@ -158,6 +165,19 @@ class FusedExpertParallel:
         gs = torch.empty((self.capacity, self.I // 128), dtype=torch.float32, device=self.dev)
         rc = lib.croq_quant_rows_e4m3_n(_v2(g), _v2(gq), _v2(gs), _v1(offsets[self.e_loc:]), stream)
         _lib.check(rc, "croq_quant_rows_e4m3_n")
+        if not self.push_results:
+            # results stay on the owner; the combine loads them over NVLink
+            api.moe_grouped_gemm_e4m3(gq, gs, w2, w2_scale, offsets, swiglu=False, out=self.y_home)
+            self._barrier()                  # every owner's outputs are complete
+            mark("expert_gemms")
+            out = torch.empty((x.shape[0], self.H), dtype=torch.bfloat16, device=self.dev)
+            rc = lib.croq_moe_combine_remote(_v1(self.peer_y), _v2(r["topk_idx"]), _v1(r["src_to_perm"]),
+                                             _v1(r["expert_offsets"]), _v1(dest_base), _v2(r["topk_w"]),
+                                             _v2(out), self.e_loc, self.capacity, stream)
+            _lib.check(rc, "croq_moe_combine_remote")
+            self._barrier()                  # peers are done reading my buffer: next step may overwrite
+            mark("combine")
+            return out
         # down projection; its epilogue stores every result row at its return address in
         # the home rank's y_home (over NVLink, while the next tiles' main loops run)
         rc = lib.croq_moe_grouped_gemm_e4m3_scatter(_v2(gq), _v2(gs), _v3(w2), _v3(w2_scale), _v1(offsets),
