@@ -565,9 +565,9 @@ def run_moe_arm(args, T, H, I):
     lg = [torch.randn((t_loc, E), generator=g, device=dev) for _ in range(2)]
 
     fused = None
-    if world > 1 and args.ep in ("fused", "fused-pull"):
+    if world > 1 and args.ep in ("fused", "fused-push"):
         from croqtile_b200.moe_ep_fused import FusedExpertParallel
-        fused = FusedExpertParallel(H, I, E, t_loc, k, push_results=(args.ep == "fused"))
+        fused = FusedExpertParallel(H, I, E, t_loc, k, push_results=(args.ep == "fused-push"))
 
     def layer(x_in, l_in, timers=None):
         if fused is not None:
@@ -692,7 +692,7 @@ def run_moe_arm(args, T, H, I):
                        "experts": E, "top_k": k, "experts_per_gpu": e_loc, "tokens_per_gpu": t_loc,
                        "parallelism": (f"ep{world}: tokens data-parallel, experts owner-partitioned, " +
                                        (("dispatch by peer stores, results pushed back by the down projection's "
-                                         "epilogue over NVLink peer memory" if args.ep == "fused" else
+                                         "epilogue over NVLink peer memory" if args.ep == "fused-push" else
                                          "dispatch by peer stores, combine by peer loads over NVLink peer memory")
                                         if fused is not None else "NCCL all-to-all dispatch/combine"))
                        if world > 1 else "single GPU",
@@ -739,9 +739,10 @@ def main():
     ap.add_argument("--impl", default="croq", choices=["croq", "reference"])
     ap.add_argument("--workload", default="fp8_blockscale_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep", default="fused", choices=["fused", "fused-pull", "nccl"],
-                    help="MoE workload at N > 1: exchange fused into the kernels (results pushed back by "
-                         "the down projection's epilogue, or pulled by the combine kernel), or NCCL all-to-all")
+    ap.add_argument("--ep", default="fused", choices=["fused", "fused-push", "nccl"],
+                    help="MoE workload at N > 1: exchange fused into the kernels (combine by peer loads; "
+                         "fused-push: results pushed back by the down projection's epilogue), or NCCL "
+                         "all-to-all")
     args = ap.parse_args()
     kind, M, N, K = WORKLOADS[args.workload]
     if kind == "moe":

@@ -9,16 +9,16 @@ symmetric (peer-mapped) memory and
     over NVLink (the local tokens are quantised once beforehand),
   * the expert GEMMs run on the owner's buffer in place (tile table from the
     device-side offsets, so no host synchronisation anywhere in the step),
-  * the down projection's epilogue stores every result row straight into the
-    home rank's ``y_home`` buffer at row t*k+j, so the transfer of the combine
-    overlaps the GEMM's main loop; what is left of the combine is a local
-    weighted sum over k consecutive rows.
+  * the combine kernel loads each expert output row from the owner's buffer
+    (default), or the down projection's epilogue stores every result row
+    straight into the home rank's buffer at row t*k+j and the combine becomes a
+    local weighted sum (``push_results=True``).
 
 The only collectives left are an 8 KB all-gather of the per-expert counts and
-two stream-ordered barriers per step (after dispatch, after the down
-projection). One process per GPU, ``torch.distributed`` (NCCL) for the plumbing;
-only plain loads and stores cross the link. The reference has no MoE and no
-multi-GPU code; this module defines the behaviour.
+three (two with pushed results) stream-ordered barriers per step. One process
+per GPU, ``torch.distributed`` (NCCL) for the plumbing; only plain loads and
+stores cross the link. The reference has no MoE and no multi-GPU code; this
+module defines the behaviour.
 """
 from __future__ import annotations
 
@@ -50,14 +50,16 @@ class FusedExpertParallel:
     ``tokens_per_rank * k`` rows; routing imbalance needs head-room (default 2x).
     A row that does not fit is reported as CROQ_ERR_INDEX by ``api.synchronize``.
 
-    push_results: True (default) lets the down projection's epilogue store each result
-    row into the home rank's buffer; False keeps the results on the owner and lets the
-    combine kernel load them over NVLink (one more buffer and one more barrier per step).
-    Both give the same bits.
+    push_results: False (default) keeps the expert outputs on the owner and lets the
+    combine kernel load them over NVLink. True lets the down projection's epilogue store
+    each result row into the home rank's buffer instead (one barrier less per step, same
+    bits). The pushed form is not the default: on two GPUs it ended two of four benchmark
+    runs with "unspecified launch failure" on one rank, the cause was not found by reading
+    the code, and it has not been run on more than one GPU since.
     """
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, tokens_per_rank: int, k: int,
-                 group=None, capacity_factor: float = 2.0, push_results: bool = True):
+                 group=None, capacity_factor: float = 2.0, push_results: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)

@@ -53,12 +53,11 @@ def worker(rank, world, port, out_dir):
     np.save(Path(out_dir) / f"out_{rank}.npy", out.view(torch.int16).cpu().numpy())
     # same layer with the exchange fused into the row kernels over peer memory, two steps in a row
     from croqtile_b200.moe_ep_fused import FusedExpertParallel
-    for tag, push in (("fused", True), ("pull", False)):
-        ep = FusedExpertParallel(x.shape[1], w2.shape[2], E, t_loc, k, push_results=push)
-        for _ in range(2):
-            fused = ep.forward(*args)
-        api.synchronize()
-        np.save(Path(out_dir) / f"{tag}_{rank}.npy", fused.view(torch.int16).cpu().numpy())
+    ep = FusedExpertParallel(x.shape[1], w2.shape[2], E, t_loc, k)
+    for _ in range(2):
+        fused = ep.forward(*args)
+    api.synchronize()
+    np.save(Path(out_dir) / f"fused_{rank}.npy", fused.view(torch.int16).cpu().numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -75,6 +74,6 @@ def test_two_rank_expert_parallel_equals_single_gpu(tmp_path):
     mp.spawn(worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     got = np.concatenate([np.load(tmp_path / f"out_{r}.npy") for r in range(2)])
     np.testing.assert_array_equal(got, full.view(torch.int16).cpu().numpy())
-    for tag in ("fused", "pull"):
+    for tag in ("fused",):
         got = np.concatenate([np.load(tmp_path / f"{tag}_{r}.npy") for r in range(2)])
         np.testing.assert_array_equal(got, full.view(torch.int16).cpu().numpy(), err_msg=tag)
