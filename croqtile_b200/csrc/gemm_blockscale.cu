@@ -554,12 +554,12 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
 // CTA is a remote mbarrier arrive on the leader's barrier.
 constexpr int kPairM = 256;
 constexpr int kPairN = 256;
-constexpr int kPairStages = 6;
+constexpr int kPairStages = 5;
 constexpr uint32_t kPairABytes = 128 * kBlockK;
 constexpr uint32_t kPairBBytes = 128 * kBlockK;
 constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes;
 constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024 +
-                                  static_cast<size_t>(kEpiWarps) * 32 * 8 * 16;  // + output staging
+                                  kOutStageBytes;   // + this CTA's 128x256 half of the output tile
 constexpr int kPairGroupM = 8;
 
 __device__ __forceinline__ void decode_pair_tile(const BlockScaleParams& p, int w, int& m0, int& n0) {
@@ -584,6 +584,9 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ __align__(8) uint64_t bar_mma_done[kPairStages];   // one per CTA (multicast commit)
   __shared__ __align__(8) uint64_t bar_part_empty[2];           // used in rank 0
   __shared__ __align__(8) uint64_t bar_drain[2];
+  __shared__ __align__(8) uint64_t bar_out_full;    // this CTA's promotion warps left their results
+  __shared__ __align__(8) uint64_t bar_out_empty;   // this CTA's store warp has read the staging area
+  __shared__ int out_staged[kEpiWarps];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
 
@@ -593,6 +596,8 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint4* const out_stage_all = reinterpret_cast<uint4*>(
+      smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes);
   const int num_kb = p.KB;
   const int my_tiles = p.total_work > pair ? (p.total_work - pair + num_pairs - 1) / num_pairs : 0;
   const int total_kb = my_tiles * num_kb;
@@ -607,6 +612,8 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&bar_part_empty[b]), 2 * kEpiWarps);   // promotion warps of both CTAs
       mbar_init(smem_u32(&bar_drain[b]), 1);
     }
+    mbar_init(smem_u32(&bar_out_full), kEpiWarps);
+    mbar_init(smem_u32(&bar_out_empty), 1);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -684,6 +691,41 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       if (elect_one()) umma_commit_pair(smem_u32(&bar_drain[buf]), 1);
       __syncwarp();
       mbar_wait(smem_u32(&bar_drain[buf]), 0, abort_ptr);
+    } else if (warp == 2) {
+      // -------------------------------------------------------- store warp --
+      // Writes this CTA's 128 rows of each finished tile from the staging area to
+      // `out`, eight lanes per 128-byte row segment, while the promotion warps
+      // already drain the next tile's partials.
+      uint32_t out_phase = 0;
+      const int c = lane & 7;
+      for (int w = pair; w < p.total_work; w += num_pairs) {
+        int m0, n0;
+        decode_pair_tile(p, w, m0, n0);
+        if (!mbar_wait(smem_u32(&bar_out_full), out_phase, abort_ptr)) break;
+        for (int ew = 0; ew < kEpiWarps; ++ew) {
+          if (out_staged[ew] == 0) continue;
+          const int row0 = m0 + static_cast<int>(rank) * 128 + (ew & 3) * 32;
+          const int rows_valid = p.M - row0;
+          const int col_base = n0 + (ew >> 2) * 128;
+          const uint4* region = out_stage_all + ew * (kOutWarpBytes / 16);
+          uint8_t* const dst0 = reinterpret_cast<uint8_t*>(p.out) +
+                                (static_cast<size_t>(row0) * p.out_ld + col_base) * 2 + c * 16;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const uint4 v0 = region[r * 8 + (c ^ (r & 7))];
+            const uint4 v1 = region[(32 + r) * 8 + (c ^ (r & 7))];
+            if (r < rows_valid) {
+              uint8_t* dst = dst0 + static_cast<size_t>(r) * p.out_ld * 2;
+              *reinterpret_cast<uint4*>(dst) = v0;
+              *reinterpret_cast<uint4*>(dst + 128) = v1;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_out_empty));
+        out_phase ^= 1u;
+      }
     }
   } else {
     // ------------------------------------------------- promotion + store --
@@ -692,9 +734,9 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const int half = (warp - 4) >> 2;
     const bool vec_ok = ((p.out_ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
-    uint4* const out_stage = reinterpret_cast<uint4*>(
-        smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) +
-        (warp - 4) * 32 * 8;
+    uint4* const region = out_stage_all + (warp - 4) * (kOutWarpBytes / 16);
+    const int swz = lane & 7;
+    uint32_t out_phase = 0;
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -739,22 +781,21 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         buf ^= 1;
       }
       if (!ok) break;
-      const int row0 = m0 + static_cast<int>(rank) * 128 + quarter * 32;
-      if (vec_ok && col_base + 128 <= p.N) {
-        uint16_t* out_block = p.out + static_cast<size_t>(row0) * p.out_ld + col_base;
+      // results: into the staging area (the store warp writes them out), or, for a ragged /
+      // unaligned block, straight to memory one row per lane
+      ok = mbar_wait(smem_u32(&bar_out_empty), out_phase ^ 1u, abort_ptr);   // previous tile drained
+      if (!ok) break;
+      out_phase ^= 1u;
+      const bool staged = vec_ok && col_base + 128 <= p.N;
+      if (staged) {
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          uint4 pk[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const int q = b * 8 + c;
-            pk[c].x = pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y);
-            pk[c].y = pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y);
-            pk[c].z = pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y);
-            pk[c].w = pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y);
-          }
-          warp_store_rows<8>(out_block + b * 64, static_cast<size_t>(p.out_ld) * 2, p.M - row0,
-                             out_stage, pk, lane);
+        for (int q = 0; q < 16; ++q) {
+          // 64-column block q / 8, 16-byte piece q % 8 of this lane's row
+          region[((q >> 3) * 32 + lane) * 8 + ((q & 7) ^ swz)] =
+              make_uint4(pack2<kBf16>(acc[q * 4 + 0].x, acc[q * 4 + 0].y),
+                         pack2<kBf16>(acc[q * 4 + 1].x, acc[q * 4 + 1].y),
+                         pack2<kBf16>(acc[q * 4 + 2].x, acc[q * 4 + 2].y),
+                         pack2<kBf16>(acc[q * 4 + 3].x, acc[q * 4 + 3].y));
         }
       } else if (row < p.M && col_base < p.N) {
         uint16_t* out_row = p.out + static_cast<size_t>(row) * p.out_ld + col_base;
@@ -763,6 +804,11 @@ gemm_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (col_base + 2 * i < p.N) out_row[2 * i] = pack1<kBf16>(acc[i].x);
           if (col_base + 2 * i + 1 < p.N) out_row[2 * i + 1] = pack1<kBf16>(acc[i].y);
         }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        out_staged[warp - 4] = staged ? 1 : 0;
+        mbar_arrive(smem_u32(&bar_out_full));   // release: the staged block and the flag are visible
       }
     }
   }
