@@ -45,7 +45,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the
 # ncu captures summarised under profiles/ (same command, same shapes)
 NCU_DRAM_TRAFFIC_BYTES = {
-    "fp8_blockscale_8192": 350.80e6 + 118.65e6,
+    "fp8_blockscale_8192": 351.85e6 + 117.85e6,
     "bf16_hilbert_8192": 1.1129e9 + 128.0e6,
     "sparse24_f16_8192": 709.02e6 + 122.42e6,
 }
