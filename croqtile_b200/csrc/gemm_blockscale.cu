@@ -76,6 +76,7 @@ constexpr int kGroupM = 16;  // M tiles per rasterisation group
 
 enum Mode : int { kDense = 0, kGrouped = 1, kGroupedSwiGLU = 2 };
 constexpr int kMaxExperts = 1024;
+constexpr int kMaxPeers = 64;   // GPUs a scattered store can address
 
 struct BlockScaleParams {
   uint16_t* out;
@@ -169,6 +170,10 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ __align__(8) uint64_t bar_out_full;    // all promotion warps left their results
   __shared__ __align__(8) uint64_t bar_out_empty;   // the store warp has read the staging area
   __shared__ int out_staged[kEpiWarps];             // 1: the warp's block is in the staging area
+  // scattered form: the tile's 128 return entries and the peers' buffer addresses, so
+  // that the store warp's per-row look-ups are shared-memory reads
+  __shared__ long long ret_s[(kMode == kGrouped) ? kBlockM : 1];
+  __shared__ unsigned long long peer_s[(kMode == kGrouped) ? kMaxPeers : 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
 
@@ -212,6 +217,9 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
       : 0;
   const int total_kb = my_tiles * num_kb;   // K blocks this CTA walks, over all its tiles
 
+  if constexpr (kMode == kGrouped) {
+    if (p.row_ret != nullptr && threadIdx.x < p.world) peer_s[threadIdx.x] = __ldg(p.peer_out + threadIdx.x);
+  }
   if (threadIdx.x == 0) {
     abort_word = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -335,6 +343,17 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
         Tile t;
         if constexpr (kMode == kDense) t = decode_dense(p, w);
         else t = decode_grouped(p, tile_prefix, offsets_s, w, kTileCols);
+        if constexpr (kMode == kGrouped) {
+          if (p.row_ret != nullptr) {
+            // return entries of the tile's rows, fetched while the tile is still being promoted
+#pragma unroll
+            for (int j = 0; j < kBlockM / 32; ++j) {
+              const int row = t.m0 + lane + 32 * j;
+              ret_s[lane + 32 * j] = row < t.m_end ? __ldg(p.row_ret + row) : -1ll;
+            }
+            __syncwarp();
+          }
+        }
         if (!mbar_wait(smem_u32(&bar_out_full), out_phase, abort_ptr)) break;
         for (int ew = 0; ew < kEpiWarps; ++ew) {
           if (out_staged[ew] == 0) continue;
@@ -352,14 +371,14 @@ gemm_blockscale_kernel(const __grid_constant__ CUtensorMap map_a,
               uint8_t* dst;
               if (kMode == kGrouped && p.row_ret != nullptr) {
                 // a return entry outside the peers' buffers is reported, never dereferenced
-                const long long ret = __ldg(p.row_ret + row0 + r);
+                const long long ret = ret_s[(ew & 3) * 32 + r];
                 const int home = static_cast<int>(ret >> 32);
                 const long long rr = ret & 0xFFFFFFFFll;
                 if (home < 0 || home >= p.world || rr >= p.peer_rows) {
                   *p.status = kDevBadIndex;
                   dst = nullptr;
                 } else {
-                  dst = reinterpret_cast<uint8_t*>(__ldg(p.peer_out + home)) +
+                  dst = reinterpret_cast<uint8_t*>(peer_s[home]) +
                         (static_cast<size_t>(rr) * p.N + col_base) * 2;
                 }
               } else {
@@ -1011,7 +1030,7 @@ int grouped_entry(const croq_view2* x, const croq_view2* x_scale, const croq_vie
   if (scatter) {
     if (swiglu) return CROQ_ERR_UNSUPPORTED;
     if (row_ret->dims[0] < R || peer_out_ptrs->dims[0] == 0 || peer_rows <= 0) return CROQ_ERR_SHAPE;
-    if (peer_out_ptrs->dims[0] > 0x7FFFFFFFull) return CROQ_ERR_SHAPE;
+    if (peer_out_ptrs->dims[0] > static_cast<size_t>(kMaxPeers)) return CROQ_ERR_UNSUPPORTED;
     if (N % 8 != 0) return CROQ_ERR_ALIGN;   // 16-byte row segments at every destination
     if ((reinterpret_cast<uintptr_t>(row_ret->ptr) & 7u) != 0 ||
         (reinterpret_cast<uintptr_t>(peer_out_ptrs->ptr) & 7u) != 0)

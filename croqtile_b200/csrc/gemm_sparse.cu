@@ -330,6 +330,13 @@ __device__ __forceinline__ void umma_sp_f16_pair(uint32_t tmem_d, uint64_t adesc
       : "memory");
 }
 
+// The pair kernel splits the 256 metadata columns into two buffers of 128 (one
+// K chunk of 4096 positions each): the repack warps fill one while the MMAs of
+// the previous chunk read the other, also across tile boundaries, so only the
+// accumulator read of the epilogue is left between two tiles' MMAs.
+constexpr int kPairChunkK = 4096;
+constexpr int kPairMetaCols = 128;
+
 template <bool kBf16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -337,8 +344,10 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kPairStages];    // used in rank 0
   __shared__ __align__(8) uint64_t bar_empty[kPairStages];   // one per CTA (multicast commit)
-  __shared__ __align__(8) uint64_t bar_meta_full;            // used in rank 0: both CTAs' metadata are in TMEM
-  __shared__ __align__(8) uint64_t bar_chunk_done;           // one per CTA (multicast commit)
+  __shared__ __align__(8) uint64_t bar_meta_full[2];   // used in rank 0: both CTAs' metadata of a chunk are in TMEM
+  __shared__ __align__(8) uint64_t bar_meta_free[2];   // one per CTA (multicast commit): the chunk's MMAs retired
+  __shared__ __align__(8) uint64_t bar_acc_full;       // one per CTA (multicast commit): the tile's MMAs retired
+  __shared__ __align__(8) uint64_t bar_acc_empty;      // used in rank 0: both CTAs have read the accumulator
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_word;
 
@@ -348,7 +357,7 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int num_chunks = (p.K + kChunkK - 1) / kChunkK;
+  const int num_chunks = (p.K + kPairChunkK - 1) / kPairChunkK;
 
   if (threadIdx.x == 0) {
     abort_word = 0;
@@ -356,8 +365,12 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    mbar_init(smem_u32(&bar_meta_full), 8);   // four repack warps in each CTA
-    mbar_init(smem_u32(&bar_chunk_done), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_meta_full[b]), 8);   // four repack warps in each CTA
+      mbar_init(smem_u32(&bar_meta_free[b]), 1);
+    }
+    mbar_init(smem_u32(&bar_acc_full), 1);
+    mbar_init(smem_u32(&bar_acc_empty), 8);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -409,15 +422,23 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                           256, 256, /*sparse=*/true);
     int stage = 0;
     uint32_t phase = 0;
-    uint32_t meta_phase = 0;
+    uint32_t acc_empty_phase = 0;
+    int g = 0;                 // chunks issued so far: metadata buffer g & 1, its use number g >> 1
+    bool first_tile = true;
     bool ok = true;
     for (int w = pair; w < p.total_work && ok; w += num_pairs) {
-      for (int c = 0; c < num_chunks && ok; ++c) {
-        const int k0 = c * kChunkK;
-        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
-        ok = mbar_wait(smem_u32(&bar_meta_full), meta_phase, abort_ptr);
+      for (int c = 0; c < num_chunks && ok; ++c, ++g) {
+        const int k0 = c * kPairChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kPairChunkK) + kBlockK - 1) / kBlockK;
+        const int mb = g & 1;
+        ok = mbar_wait(smem_u32(&bar_meta_full[mb]), static_cast<uint32_t>(g >> 1) & 1u, abort_ptr);
         if (!ok) break;
-        meta_phase ^= 1u;
+        if (c == 0 && !first_tile) {
+          // the previous tile's accumulator has been read by both CTAs
+          ok = mbar_wait(smem_u32(&bar_acc_empty), acc_empty_phase, abort_ptr);
+          if (!ok) break;
+          acc_empty_phase ^= 1u;
+        }
         tc_fence_after_sync();
         for (int kb = 0; kb < kb_in_chunk; ++kb) {
           ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr);
@@ -427,7 +448,8 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint64_t adesc = umma_desc_k_sw128(a_src);
           const uint64_t bdesc0 = umma_desc_k_sw128(a_src + kPairABytes);
           const uint64_t bdesc1 = umma_desc_k_sw128(a_src + kPairABytes + kPairBHalfBytes);
-          const uint32_t tmem_e = tmem_base + static_cast<uint32_t>(kMetaCol0 + 4 * kb);
+          const uint32_t tmem_e =
+              tmem_base + static_cast<uint32_t>(kMetaCol0 + mb * kPairMetaCols + 4 * kb);
           if (elect_one()) {
             umma_sp_f16_pair(tmem_base, adesc, bdesc0, tmem_e, idesc, (c | kb) != 0 ? 1u : 0u);
             umma_sp_f16_pair(tmem_base, adesc + 2u, bdesc0 + 4u, tmem_e, idesc | 1u, 1u);
@@ -438,8 +460,12 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (elect_one()) umma_commit_pair(smem_u32(&bar_chunk_done), 3);
+        if (elect_one()) {
+          umma_commit_pair(smem_u32(&bar_meta_free[mb]), 3);
+          if (c == num_chunks - 1) umma_commit_pair(smem_u32(&bar_acc_full), 3);
+        }
       }
+      first_tile = false;
     }
   } else if (warp >= 4) {
     // ------------------------------------------ metadata repack + epilogue --
@@ -450,14 +476,16 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool vec_ok = ((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     const size_t meta_pitch = static_cast<size_t>(p.K) / 8;
-    uint32_t done_phase = 0;
-    bool pending = false;
+    uint32_t acc_full_phase = 0;
+    int g = 0;
     bool ok = true;
     int prev_m0 = 0, prev_n0 = 0;
     bool have_prev_tile = false;
 
     uint4* const out_stage = reinterpret_cast<uint4*>(
         smem_raw + (smem_base - smem_u32(smem_raw)) + kPairStages * kPairStageBytes) + quarter * 256;
+    // Accumulator of the finished tile -> memory; returns after the TMEM reads, so the
+    // caller can hand the accumulator back.
     auto epilogue = [&](int m0, int n0) {
       tmem_store_rows<kBf16, 256>(tmem_base + lane_field, p.out, static_cast<size_t>(p.N),
                                   m0 + static_cast<int>(rank) * 128 + quarter * 32, p.M, n0, p.N,
@@ -471,17 +499,15 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int r_lo = m0 + static_cast<int>(rank) * 128 + row_lo_in_tile, r_hi = r_lo + 8;
       const uint8_t* meta_lo = p.meta + static_cast<size_t>(min(r_lo, p.M - 1)) * meta_pitch;
       const uint8_t* meta_hi = p.meta + static_cast<size_t>(min(r_hi, p.M - 1)) * meta_pitch;
-      for (int c = 0; c < num_chunks; ++c) {
-        if (pending) {
-          ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
-          if (!ok) break;
-          done_phase ^= 1u;
-          tc_fence_after_sync();
-          pending = false;
-          if (c == 0 && have_prev_tile) epilogue(prev_m0, prev_n0);
-        }
-        const int k0 = c * kChunkK;
-        const int kb_in_chunk = (min(p.K - k0, kChunkK) + kBlockK - 1) / kBlockK;
+      for (int c = 0; c < num_chunks; ++c, ++g) {
+        const int mb = g & 1;
+        // the MMAs that read this buffer two chunks ago have retired (passes at once for
+        // the first use of each buffer)
+        ok = mbar_wait(smem_u32(&bar_meta_free[mb]), (static_cast<uint32_t>(g >> 1) & 1u) ^ 1u, abort_ptr);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const int k0 = c * kPairChunkK;
+        const int kb_in_chunk = (min(p.K - k0, kPairChunkK) + kBlockK - 1) / kBlockK;
         for (int kb = 0; kb < kb_in_chunk; ++kb) {
           const size_t off = static_cast<size_t>(k0) / 8 + static_cast<size_t>(kb) * 16;
           const bool first_ok = off + 8 <= meta_pitch, second_ok = off + 16 <= meta_pitch;
@@ -498,24 +524,34 @@ gemm_sparse_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t hi16 = khalf ? (h[s] >> 16) : (h[s] & 0xFFFFu);
             wd[s] = lo16 | (hi16 << 16);
           }
-          tmem_st_32x32_x4(tmem_base + lane_field + static_cast<uint32_t>(kMetaCol0 + 4 * kb), wd[0],
-                           wd[1], wd[2], wd[3]);
+          tmem_st_32x32_x4(tmem_base + lane_field +
+                               static_cast<uint32_t>(kMetaCol0 + mb * kPairMetaCols + 4 * kb),
+                           wd[0], wd[1], wd[2], wd[3]);
         }
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_meta_full), 0));
-        pending = true;
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_meta_full[mb]), 0));
+        if (c == 0 && have_prev_tile) {
+          // this tile's first chunk is fed; now drain the previous tile's accumulator
+          ok = mbar_wait(smem_u32(&bar_acc_full), acc_full_phase, abort_ptr);
+          if (!ok) break;
+          acc_full_phase ^= 1u;
+          tc_fence_after_sync();
+          epilogue(prev_m0, prev_n0);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty), 0));
+        }
       }
       prev_m0 = m0;
       prev_n0 = n0;
       have_prev_tile = true;
     }
-    if (ok && pending) {
-      ok = mbar_wait(smem_u32(&bar_chunk_done), done_phase, abort_ptr);
+    if (ok && have_prev_tile) {
+      ok = mbar_wait(smem_u32(&bar_acc_full), acc_full_phase, abort_ptr);
       if (ok) {
         tc_fence_after_sync();
-        if (have_prev_tile) epilogue(prev_m0, prev_n0);
+        epilogue(prev_m0, prev_n0);
       }
     }
   }
