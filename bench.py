@@ -47,7 +47,7 @@ WORKLOADS = {
 NCU_DRAM_TRAFFIC_BYTES = {
     "fp8_blockscale_8192": 351.85e6 + 117.85e6,
     "bf16_hilbert_8192": 1.1129e9 + 128.0e6,
-    "sparse24_f16_8192": 709.02e6 + 122.42e6,
+    "sparse24_f16_8192": 781.05e6 + 124.69e6,
 }
 NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0, "sparse": 4500.0, "moe": 4500.0}
 MOE_EXPERTS, MOE_TOPK = 256, 8
