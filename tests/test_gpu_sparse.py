@@ -81,19 +81,21 @@ def test_random_structured_inputs(oracle, shape):
     assert max_rel_err(got, ref, floor=0.05 * np.sqrt(K)) <= 5e-3
 
 
-def test_config4_full_size_sampled_rows(oracle):
-    """8192^3: sampled rows against the oracle and a checksum of row sums."""
-    n = 8192
+@pytest.mark.parametrize("n,k", [(8192, 8192), (4096, 8192 + 128)])
+def test_config4_full_size_sampled_rows(oracle, n, k):
+    """8192^3 (config 4), and a shape with an odd number of 4096-wide metadata chunks per
+    tile and several tiles per CTA pair (the chunk buffers then alternate across tiles):
+    sampled rows against the oracle."""
     rng = np.random.default_rng(4001)
-    rows = np.array([0, 7, 8, 15, 16, 127, 128, 4100, 8191])
-    dense_rows = random_24(rng, len(rows), n)
+    rows = np.array([0, 7, 8, 15, 16, 127, 128, n // 2 + 4, n - 1])
+    dense_rows = random_24(rng, len(rows), k)
     g = torch.Generator(device="cuda").manual_seed(4002)
-    rhs = (torch.rand((n, n), generator=g, device="cuda") * 2 - 1).to(torch.float16)
+    rhs = (torch.rand((n, k), generator=g, device="cuda") * 2 - 1).to(torch.float16)
     # device-side structured A: two kept values per group at random positions
-    vals = (torch.rand((n, n // 2), generator=g, device="cuda") * 2 - 1).to(torch.float16)
+    vals = (torch.rand((n, k // 2), generator=g, device="cuda") * 2 - 1).to(torch.float16)
     vals[vals == 0] = 1.0
-    first = torch.randint(0, 3, (n, n // 4), generator=g, device="cuda")
-    gap = torch.randint(1, 4, (n, n // 4), generator=g, device="cuda")
+    first = torch.randint(0, 3, (n, k // 4), generator=g, device="cuda")
+    gap = torch.randint(1, 4, (n, k // 4), generator=g, device="cuda")
     second = torch.minimum(first + gap, torch.full_like(first, 3))
     nib = (first | (second << 2)).to(torch.uint8)
     meta = (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous()
@@ -106,7 +108,7 @@ def test_config4_full_size_sampled_rows(oracle):
     api.synchronize()
     ref = oracle.gemm_row_row(oracle.f16_to_f32(bits), oracle.f16_to_f32(bits_of(rhs)), tile=(16, 256, 64))
     got = oracle.f16_to_f32(bits_of(out[torch.from_numpy(rows).cuda()]))
-    assert max_rel_err(got, ref, floor=0.05 * np.sqrt(n)) <= 5e-3
+    assert max_rel_err(got, ref, floor=0.05 * np.sqrt(k)) <= 5e-3
     assert torch.isfinite(out.float()).all()
 
 
