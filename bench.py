@@ -643,10 +643,16 @@ def run_moe_arm(args, T, H, I):
     kernels = None
     if world == 1:
         # per-kernel device times of one layer (CUDA events around each call)
+        ballast = torch.empty(1 << 28, dtype=torch.float32, device=dev)    # 1 GiB
+
         def timed(fn, reps=5):
+            """Device time per call: the calls are enqueued behind ~1.5 ms of unrelated work,
+            so the host's launch overhead is hidden and the events bracket back-to-back kernels."""
             fn()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            for _ in range(3):
+                ballast.normal_()
             a.record()
             for _ in range(reps):
                 out = fn()
@@ -678,6 +684,7 @@ def run_moe_arm(args, T, H, I):
             "grouped_gemm_down": {"ms": ms_g2, "TFLOP/s": 2.0 * rows * H * I / (ms_g2 * 1e-3) / 1e12},
             "unpermute": bw(rows * 2 * H + T * 2 * H + rows * 8, ms_un),
         }
+        del ballast
         api.synchronize()
 
     if rank == 0:
