@@ -58,8 +58,25 @@ def worker(rank, world, port, out_dir):
         fused = ep.forward(*args)
     api.synchronize()
     np.save(Path(out_dir) / f"fused_{rank}.npy", fused.view(torch.int16).cpu().numpy())
+    # N-sharded GEMM with the replicated output gathered over NCCL (row-major and transposed)
+    from croqtile_b200.nshard import matmul_nsharded, shard_range
+    lhs, rhs = gemm_problem(torch.device("cuda", rank))
+    lo, hi = shard_range(rhs.shape[0], world, rank)
+    shard = rhs[lo:hi].contiguous()
+    full = matmul_nsharded(lhs, shard, rhs.shape[0], gather_output="row_major")
+    full_t = matmul_nsharded(lhs, shard, rhs.shape[0], gather_output="transposed")
+    api.synchronize()
+    np.save(Path(out_dir) / f"gemm_{rank}.npy", full.view(torch.int16).cpu().numpy())
+    np.save(Path(out_dir) / f"gemm_t_{rank}.npy", full_t.view(torch.int16).cpu().numpy())
     dist.barrier()
     dist.destroy_process_group()
+
+
+def gemm_problem(device):
+    g = torch.Generator(device=device).manual_seed(77)
+    lhs = torch.randn((300, 512), generator=g, device=device).to(torch.bfloat16)
+    rhs = torch.randn((1000, 512), generator=g, device=device).to(torch.bfloat16)   # slabs [0,512) and [512,1000)
+    return lhs, rhs
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -77,3 +94,11 @@ def test_two_rank_expert_parallel_equals_single_gpu(tmp_path):
     for tag in ("fused",):
         got = np.concatenate([np.load(tmp_path / f"{tag}_{r}.npy") for r in range(2)])
         np.testing.assert_array_equal(got, full.view(torch.int16).cpu().numpy(), err_msg=tag)
+    # the gathered N-sharded product equals the single-GPU product bit for bit on every rank
+    lhs, rhs = gemm_problem(torch.device("cuda", 0))
+    want = api.matmul(lhs, rhs)
+    api.synchronize()
+    want_bits = want.view(torch.int16).cpu().numpy()
+    for r in range(2):
+        np.testing.assert_array_equal(np.load(tmp_path / f"gemm_{r}.npy"), want_bits)
+        np.testing.assert_array_equal(np.load(tmp_path / f"gemm_t_{r}.npy"), want_bits.T)
