@@ -426,7 +426,8 @@ def run_croq_arm(args, kind, M, N, K):
                 "nominal_peak": NOMINAL_PEAK_TFLOPS[kind],
                 "kernel": {"blockscale": "gemm_blockscale_pair_kernel", "sparse": "gemm_sparse_pair_kernel"}.get(
                     kind, "gemm_dense_pair_kernel"),
-                "launch_ms_mean": launch_ms, "launch_ms_min": float(per_step.min()),
+                "launch_ms_mean": launch_ms, "launch_ms_median": float(np.median(per_step)),
+                "launch_ms_min": float(per_step.min()),
             },
         }
         if kind == "sparse" and world == 1:
