@@ -69,6 +69,7 @@ SIGNATURES = {
     "croq_moe_grouped_gemm_e4m3": (c_int, [P2, P2, P3, P3, P1, P2, c_int, c_void_p]),
     "croq_quant_rows_e4m3": (c_int, [P2, P2, P2, c_void_p]),
     "croq_quant_rows_e4m3_n": (c_int, [P2, P2, P2, P1, c_void_p]),
+    "croq_moe_ep_placement": (c_int, [P2, c_int, P1, P1, c_void_p]),
     "croq_moe_dispatch_quant_e4m3": (c_int, [P2, P1, P2, P1, P1, P1, P1, c_int, c_int, c_void_p]),
     "croq_moe_dispatch_rows_q_e4m3": (c_int, [P2, P2, P1, P2, P1, P1, P1, P1, P1, c_int, c_int, c_int,
                                               c_void_p]),

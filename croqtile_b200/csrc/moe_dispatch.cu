@@ -162,6 +162,46 @@ moe_dispatch_rows_q_kernel(const uint8_t* __restrict__ q_src, const float* __res
   }
 }
 
+// Placement of this rank's rows in the owners' buffers from the all-gathered
+// per-expert counts (counts[s][e] = rows rank s sends to expert e). One CTA:
+//   total[e]      = sum_s counts[s][e]
+//   start[e]      = rows of the owner's earlier experts (exclusive prefix of total inside
+//                   the owner's group of experts_per_rank experts)
+//   dest_base[e]  = start[e] + sum_{s < rank} counts[s][e]
+//   offsets[i]    = exclusive prefix of total over THIS rank's experts (length e_loc + 1):
+//                   the expert_offsets of the owner-side grouped GEMMs.
+constexpr int kPlacementMaxExperts = 1024;
+
+__global__ void __launch_bounds__(256)
+moe_ep_placement_kernel(const int* __restrict__ counts, int world, int E, int rank,
+                        int experts_per_rank, int* __restrict__ dest_base,
+                        int* __restrict__ offsets) {
+  __shared__ int total_s[kPlacementMaxExperts];
+  __shared__ int before_s[kPlacementMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int total = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = counts[static_cast<size_t>(s) * E + e];
+      total += c;
+      if (s < rank) before += c;
+    }
+    total_s[e] = total;
+    before_s[e] = before;
+  }
+  __syncthreads();
+  // one thread per owner walks its experts in order (experts_per_rank is small)
+  for (int owner = threadIdx.x; owner < world; owner += blockDim.x) {
+    int run = 0;
+    for (int i = 0; i < experts_per_rank; ++i) {
+      const int e = owner * experts_per_rank + i;
+      dest_base[e] = run + before_s[e];
+      if (owner == rank) offsets[i] = run;
+      run += total_s[e];
+    }
+    if (owner == rank) offsets[experts_per_rank] = run;
+  }
+}
+
 // out[t,:] = RN_bf16( sum_j w[t,j] * y_owner(t,j)[row(t,j), :] ), ascending j.
 template <int kMaxK>
 __global__ void __launch_bounds__(kRowThreads)
@@ -305,6 +345,27 @@ int croq_moe_dispatch_rows_q_e4m3(const croq_view2* q_src, const croq_view2* sca
       peer_ret_ptrs != nullptr ? static_cast<const unsigned long long*>(peer_ret_ptrs->ptr) : nullptr,
       my_rank, static_cast<int>(k), static_cast<int>(T), static_cast<int>(E), static_cast<int>(rows),
       experts_per_rank, capacity_rows, static_cast<int>(H), static_cast<int>(SB), st->status_dev);
+  CROQ_CUDA_TRY(cudaGetLastError());
+  return CROQ_OK;
+}
+
+int croq_moe_ep_placement(const croq_view2* counts, int rank, const croq_view1* dest_base,
+                          const croq_view1* owner_offsets, croq_stream stream_) {
+  using namespace croq;
+  clear_error();
+  if (!view_ok(counts) || !view_ok(dest_base) || !view_ok(owner_offsets)) return CROQ_ERR_NULL;
+  const size_t W = counts->dims[0], E = counts->dims[1];
+  if (W == 0 || E == 0 || E % W != 0) return CROQ_ERR_SHAPE;
+  if (E > static_cast<size_t>(kPlacementMaxExperts)) return CROQ_ERR_UNSUPPORTED;
+  if (rank < 0 || static_cast<size_t>(rank) >= W) return CROQ_ERR_SHAPE;
+  if (dest_base->dims[0] != E || owner_offsets->dims[0] != E / W + 1) return CROQ_ERR_SHAPE;
+  int rc = CROQ_OK;
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  moe_ep_placement_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const int*>(counts->ptr), static_cast<int>(W), static_cast<int>(E), rank,
+      static_cast<int>(E / W), static_cast<int*>(dest_base->ptr),
+      static_cast<int*>(owner_offsets->ptr));
   CROQ_CUDA_TRY(cudaGetLastError());
   return CROQ_OK;
 }

@@ -135,14 +135,10 @@ class FusedExpertParallel:
         # counts of every rank -> placement of my rows in the owners' buffers (all on the device)
         counts = torch.empty((self.world, E), dtype=torch.int32, device=self.dev)
         dist.all_gather_into_tensor(counts, r["expert_counts"], group=self.group)
-        total = counts.sum(0, dtype=torch.int32)                                  # rows per expert, all sources
-        per_owner = total.view(self.world, self.e_loc)
-        expert_start = (per_owner.cumsum(1, dtype=torch.int32) - per_owner).reshape(-1)   # inside the owner
-        before_me = counts[: self.rank].sum(0, dtype=torch.int32)                 # rows of lower source ranks
-        dest_base = (expert_start + before_me).contiguous()
-        mine = total[self.rank * self.e_loc:(self.rank + 1) * self.e_loc]
-        offsets = torch.zeros(self.e_loc + 1, dtype=torch.int32, device=self.dev)
-        offsets[1:] = mine.cumsum(0, dtype=torch.int32)
+        dest_base = torch.empty((E,), dtype=torch.int32, device=self.dev)
+        offsets = torch.empty((self.e_loc + 1,), dtype=torch.int32, device=self.dev)
+        rc = lib.croq_moe_ep_placement(_v2(counts), self.rank, _v1(dest_base), _v1(offsets), stream)
+        _lib.check(rc, "croq_moe_ep_placement")
         mark("counts+placement")
 
         # quantise the local tokens once, then send e4m3 rows (each token goes to k owners)

@@ -271,6 +271,13 @@ int croq_quant_rows_e4m3_n(const croq_view2* x, const croq_view2* q, const croq_
  * buffer (this rank's own included). capacity_rows: rows each buffer holds; a
  * row that would fall outside sets CROQ_ERR_INDEX. ---- */
 
+/* Placement from the all-gathered counts: counts s32 [world, E] (row s = the
+ * expert_counts of rank s) -> dest_base s32 [E] for this rank (see above) and
+ * owner_offsets s32 [E/world + 1], the expert_offsets of the rows this rank
+ * receives for its own experts (what the owner-side grouped GEMMs take). */
+int croq_moe_ep_placement(const croq_view2* counts, int rank, const croq_view1* dest_base,
+                          const croq_view1* owner_offsets, croq_stream stream);
+
 /* Dispatch: gather + 1x128 e4m3 quantiser (as croq_moe_permute_quant_e4m3)
  * writing each row and its scales into the owner's q [capacity,H] e4m3 and
  * scale [capacity,H/128] f32 buffers with peer stores. */

@@ -87,6 +87,10 @@ def test_argument_checks_run_before_any_cuda_call(croq):
     assert mx(good[0], good[1], v2(P, 64, 48), None, None, 256, 256, 2, None, None) == 8        # in dtype
     assert mx(good[0], good[1], v2(P, 64, 48), None, None, 256, 256, 0, epi(2, 1), None) == 2   # transposed: [N,M]
     assert mx(good[0], good[1], v2(P + 2, 64, 48), None, None, 256, 256, 0, epi(2, 0), None) == 3  # f32 alignment
+    pl = croq.croq_moe_ep_placement
+    assert pl(v2(P, 2, 8), 2, v1(P, 8), v1(P, 5), None) == 2        # rank outside the world
+    assert pl(v2(P, 3, 8), 0, v1(P, 8), v1(P, 5), None) == 2        # experts do not divide over ranks
+    assert pl(v2(P, 2, 8), 0, v1(P, 8), v1(P, 4), None) == 2        # offsets are [E/world + 1]
     enc = croq.croq_sparse24_encode_f16
     assert enc(v2(P, 16, 64), v2(P, 16, 32), None, None) == 1
     assert enc(v2(P, 16, 60), v2(P, 16, 30), v2(P, 16, 7), None) == 2       # K % 8

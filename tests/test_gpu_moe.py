@@ -243,6 +243,15 @@ def test_exchange_kernels_with_two_virtual_ranks_reproduce_the_layer():
         rt = routes[r]
         base = (expert_start + counts[:r].sum(0, dtype=torch.int32)).contiguous()
         bases.append(base)
+        # the placement kernel gives the same table and the owner-side offsets
+        base_k = torch.empty((E,), dtype=torch.int32, device=dev)
+        off_k = torch.empty((e_loc + 1,), dtype=torch.int32, device=dev)
+        _lib.check(lib.croq_moe_ep_placement(_v2(counts.contiguous()), r, _v1(base_k), _v1(off_k), stream),
+                   "ep_placement")
+        api.synchronize()
+        assert torch.equal(base_k, base)
+        mine_r = total[r * e_loc:(r + 1) * e_loc]
+        assert torch.equal(off_k[1:], mine_r.cumsum(0, dtype=torch.int32)) and int(off_k[0]) == 0
         xq0, xs0 = api.quant_rows_e4m3(xs[r])
         _lib.check(lib.croq_moe_dispatch_rows_q_e4m3(
             _v2(xq0), _v2(xs0), _v1(rt["perm_to_src"]), _v2(rt["topk_idx"]), _v1(rt["expert_offsets"]),
