@@ -1,0 +1,43 @@
+// The 1x128 e4m3 activation quantiser shared by the row kernels: one thread owns
+// a chunk of 8 consecutive bf16 values (16 bytes), the 16 lanes that share a
+// 128-wide block reduce |x| max by shuffles, scale = amax / 448 (1 for an
+// all-zero block) and q = RN_e4m3(x / scale) with IEEE division and
+// saturation, so the bytes are reproducible on a CPU. Callers must keep whole
+// 16-lane groups active together (row length a multiple of 128).
+#pragma once
+
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace croq {
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+__device__ __forceinline__ uint2 quant_chunk_e4m3(const uint4 raw, float& scale_out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float x[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = bf16_bits_to_f32(w[i] & 0xFFFFu);
+    x[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const unsigned group = 0xFFFFu << (threadIdx.x & 16);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group, amax, o));
+  const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[4 + i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  }
+  scale_out = scale;
+  return make_uint2(lo, hi);
+}
+
+}  // namespace croq

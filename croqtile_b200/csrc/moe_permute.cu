@@ -14,16 +14,13 @@
 
 #include "croq_device.cuh"
 #include "croq_host.h"
+#include "croq_quant.cuh"
 
 namespace croq {
 
 namespace {
 
 constexpr int kRowThreads = 256;
-
-__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
-  return __uint_as_float(bits16 << 16);
-}
 
 // dst[pos,:] = src[perm_to_src[pos] / k, :]   (perm == nullptr: identity rows)
 __global__ void __launch_bounds__(kRowThreads)
@@ -111,27 +108,8 @@ moe_permute_q_kernel(const uint8_t* __restrict__ q_src, const float* __restrict_
 
 __device__ __forceinline__ void quant_chunk(const uint4 raw, uint2* q_dst, float* scale_dst,
                                             bool write_scale) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  float x[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x[2 * i] = bf16_bits_to_f32(w[i] & 0xFFFFu);
-    x[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
-  }
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  const unsigned group = 0xFFFFu << (threadIdx.x & 16);
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(group, amax, o));
-  const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-    hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(x[4 + i] / scale, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-  }
-  *q_dst = make_uint2(lo, hi);
+  float scale;
+  *q_dst = quant_chunk_e4m3(raw, scale);
   if (write_scale) *scale_dst = scale;
 }
 
