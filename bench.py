@@ -41,6 +41,9 @@ WORKLOADS = {
     "sparse24_f16_8192": ("sparse", 8192, 8192, 8192),
     # MoE layer, DeepSeek-V3 shape: T tokens (global), hidden, expert intermediate
     "moe_deepseek_v3": ("moe", 16384, 7168, 2048),
+    # one GPU's share of that layer at 8-way expert parallelism (32 experts, 2048 tokens): small
+    # enough (1.4 GB of weights) for profiler captures
+    "moe_deepseek_v3_ep8_share": ("moe", 2048, 7168, 2048),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the
 # ncu captures summarised under profiles/ (same command, same shapes)
@@ -51,6 +54,7 @@ NCU_DRAM_TRAFFIC_BYTES = {
 }
 NOMINAL_PEAK_TFLOPS = {"blockscale": 4500.0, "dense": 2250.0, "sparse": 4500.0, "moe": 4500.0}
 MOE_EXPERTS, MOE_TOPK = 256, 8
+MOE_EXPERTS_OF = {"moe_deepseek_v3_ep8_share": 32}
 
 
 def load_peaks():
@@ -541,7 +545,7 @@ def run_moe_arm(args, T, H, I):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    E, k = MOE_EXPERTS, MOE_TOPK
+    E, k = MOE_EXPERTS_OF.get(args.workload, MOE_EXPERTS), MOE_TOPK
     e_loc, t_loc = E // world, T // world
 
     def quant_weights(n, kk, seed):
@@ -704,7 +708,8 @@ def run_moe_arm(args, T, H, I):
                                          "dispatch by peer stores, combine by peer loads over NVLink peer memory")
                                         if fused is not None else "NCCL all-to-all dispatch/combine"))
                        if world > 1 else "single GPU",
-                       "l2": "expert weights (11.3 GB / world) stream from HBM every step; two token sets alternate"},
+                       "l2": f"expert weights ({E * 3 * I * H / 1e9:.1f} GB / world) stream from HBM every step; "
+                             "two token sets alternate"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": t_loc * (H * 2 + E * 4),
                     "d2h_bytes_per_step": t_loc * H * 2, "steps": e2e_steps},
