@@ -53,9 +53,9 @@ class FusedExpertParallel:
     push_results: False (default) keeps the expert outputs on the owner and lets the
     combine kernel load them over NVLink. True lets the down projection's epilogue store
     each result row into the home rank's buffer instead (one barrier less per step, same
-    bits). The pushed form is not the default: on two GPUs it ended two of four benchmark
-    runs with "unspecified launch failure" on one rank, the cause was not found by reading
-    the code, and it has not been run on more than one GPU since.
+    bits). The pushed form is not the default: on two GPUs it ended most benchmark runs
+    with "unspecified launch failure" on one rank after several back-to-back steps, and the
+    cause has not been found; do not enable it outside single-GPU tests.
     """
 
     def __init__(self, hidden: int, intermediate: int, num_experts: int, tokens_per_rank: int, k: int,
