@@ -145,7 +145,7 @@ __device__ __forceinline__ Tile decode_grouped(const BlockScaleParams& p, const 
   Tile t;
   t.expert = e;
   t.m0 = offsets_s[e] + mt * kBlockM;
-  t.m_end = offsets_s[e + 1];
+  t.m_end = min(offsets_s[e + 1], p.M);   // offsets beyond the row count never reach memory
   t.n0 = nt * cols_per_tile;
   return t;
 }
