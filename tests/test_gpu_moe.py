@@ -307,3 +307,18 @@ def test_exchange_kernels_with_two_virtual_ranks_reproduce_the_layer():
     api.synchronize()
     for a, b in zip(before, y_home):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))    # same rows rewritten, nothing else
+
+
+def test_grouped_gemm_offsets_beyond_the_buffer_never_reach_memory(oracle):
+    """Expert offsets that claim more rows than the activation buffer holds (a receive
+    buffer that overflowed): rows inside the buffer are computed, nothing is written past it."""
+    rng = np.random.default_rng(31)
+    x, xs, w, ws, offsets = grouped_case(oracle, rng, [128, 72], 256, 256)      # 200 rows
+    claimed = np.array([0, 128, 300], np.int32)                                   # 100 rows too many
+    slab = torch.full((200 + 128, 256), -7.0, dtype=torch.bfloat16, device="cuda")
+    out = slab[:200]
+    api.moe_grouped_gemm_e4m3(to_dev_e4m3(x), to_dev(xs), to_dev_e4m3(w), to_dev(ws), to_dev(claimed), out=out)
+    api.synchronize()
+    ref = oracle.bf16_to_f32(oracle.moe_grouped_gemm_e4m3(x, xs, w, ws, offsets, False))
+    assert max_rel_err(oracle.bf16_to_f32(bits_of(out)), ref, floor=0.05) <= 2e-2
+    assert (slab[200:] == -7.0).all()
