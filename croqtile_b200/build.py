@@ -75,6 +75,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
             "-o", str(LIB_PATH), *map(str, objs), "-cudart", "static"]
     subprocess.run(link, check=True)
+    # The same objects as a static archive, for hosts that link the library into their own
+    # binary the way the reference's `--lib` mode output is linked
+    # (Documents/Documentation/lib-mode.md:67-160); such a host links with nvcc, or adds
+    # -lcudart_static -lcudadevrt -ldl -lpthread -lrt itself.
+    archive = LIB_PATH.with_suffix(".a")
+    archive.unlink(missing_ok=True)
+    ar = shutil.which("ar")
+    if ar is not None:
+        subprocess.run([ar, "rcs", str(archive), *map(str, objs)], check=True)
     return LIB_PATH
 
 

@@ -191,4 +191,30 @@ inline int sparse24_prepack_v2(const VM& meta_u8, const VW& meta_u32, croq_strea
 
 }  // namespace croq_b200
 
+// at::Tensor arguments, as the reference's runtime offers for its views
+// (runtime/choreo.h:1036-1058): define CROQ_WITH_TORCH before including this
+// header (libtorch's headers must be on the include path). `view_of<Rank>(t)`
+// checks what the library requires of a tensor (CUDA, dense row-major, rank) and
+// yields a view every function above accepts.
+#ifdef CROQ_WITH_TORCH
+#include <ATen/ATen.h>
+
+#include <stdexcept>
+
+namespace croq_b200 {
+
+template <size_t Rank>
+inline span_view<void, Rank> view_of(const at::Tensor& t) {
+  if (!t.is_cuda()) throw std::invalid_argument("croq_b200: device tensors only");
+  if (!t.is_contiguous()) throw std::invalid_argument("croq_b200: dense row-major tensors only");
+  if (static_cast<size_t>(t.dim()) != Rank) throw std::invalid_argument("croq_b200: tensor rank");
+  span_view<void, Rank> v;
+  v.ptr = t.data_ptr();
+  for (size_t i = 0; i < Rank; ++i) v.dims[i] = static_cast<size_t>(t.size(static_cast<int64_t>(i)));
+  return v;
+}
+
+}  // namespace croq_b200
+#endif  // CROQ_WITH_TORCH
+
 #endif  // CROQ_B200_HPP_

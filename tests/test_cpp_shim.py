@@ -66,3 +66,26 @@ template <class T, size_t R> struct ref_view : choreo::spanned_view<T, R> {
     build_and_run(tmp_path, "ref", prolog, "ref_view<choreo::f16, 2>", "ref_view<choreo::s32, 1>",
                   "(choreo::f16*)nullptr", "(choreo::s32*)nullptr",
                   [f"-I{REF_RUNTIME}", "-D__CHOREO_TARGET_CC__"])
+
+
+def test_shim_accepts_torch_tensors(tmp_path):
+    """CROQ_WITH_TORCH: at::Tensor arguments through view_of<Rank> (the counterpart of the
+    reference's torch overloads, runtime/choreo.h:1036-1058). Compile-only: the adapter is a
+    header template and needs libtorch's headers, which ship with the torch wheel."""
+    import torch
+    inc = Path(torch.__file__).parent / "include"
+    if not (inc / "ATen" / "ATen.h").exists():
+        pytest.skip("torch headers not installed")
+    src = tmp_path / "torch_shim.cpp"
+    src.write_text('''
+#define CROQ_WITH_TORCH
+#include "croq_b200.hpp"
+int run(const at::Tensor& a, const at::Tensor& b, const at::Tensor& c) {
+  return croq_b200::matmul_f16_ws_1p3c_persis(croq_b200::view_of<2>(a), croq_b200::view_of<2>(b),
+                                              croq_b200::view_of<2>(c));
+}
+''')
+    cmd = ["g++", "-std=c++17", "-fsyntax-only", "-w", f"-I{ROOT / 'include'}", f"-I{inc}",
+           f"-I{inc / 'torch' / 'csrc' / 'api' / 'include'}", "-I/usr/local/cuda/include", str(src)]
+    out = subprocess.run(cmd, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr[-2000:]
